@@ -10,7 +10,8 @@ Here the storage is paged. A slot is a small integer a sequence holds from its f
 step until it ends. Each position of the run order (a "schedule entry") asks for
 what its mixer needs:
 
-* `KVRequest(kv_heads, head_dim, window)`: keys and values per token. Entries with
+* `KVRequest(kv_heads, head_dim, window, value_dim)`: keys and values per token (`value_dim` 0: key rows
+  only, for mixers whose values are part of what they keep as keys). Entries with
   equal requests form a group with storage of its own,
   K and V `[entries, pages, kv_heads, page_size, head_dim]`. A sequence holds pages of
   `page_size` tokens in each group, found through the group's block table
@@ -50,6 +51,8 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None   # None: as wide as the keys; 0: no values are kept (a mixer whose values
+                                      # are part of its key rows, such as a cached latent)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -87,8 +90,9 @@ class KVGroup:
         # score is replaced whatever it was). The pools start zero-filled, and the values of a
         # page that has been used are cleared when it is handed out again (`clear_used`): what
         # an earlier sequence left, were it ever an infinity or a NaN, must not reach the next.
+        value_dim = request.head_dim if request.value_dim is None else request.value_dim
         self.keys = torch.zeros(shape, dtype=dtype, device=device)
-        self.values = torch.zeros(shape, dtype=dtype, device=device)
+        self.values = torch.zeros(shape[:-1] + (value_dim,), dtype=dtype, device=device)
         self.used = np.zeros(n_pages, dtype=bool)       # pages that have been handed out before
         # One row more than there are slots: the padding slot's (all zeros, never filled in).
         self.table_host = np.zeros((n_slots + 1, self.pages_per_sequence), dtype=np.int32)
@@ -110,7 +114,8 @@ class KVGroup:
             stop = start + 1
             while stop < len(again) and again[stop] == again[stop - 1] + 1:
                 stop += 1
-            self.values[:, again[start]:again[stop - 1] + 1].zero_()
+            # without values of their own the key rows are what gets multiplied by a zero weight
+            (self.values if self.values.shape[-1] else self.keys)[:, again[start]:again[stop - 1] + 1].zero_()
             start = stop
 
     def pages_for(self, length: int) -> int:
@@ -118,7 +123,7 @@ class KVGroup:
         return min(needed, self.ring_pages) if self.ring_pages else needed
 
     def bytes(self) -> int:
-        return 2 * self.keys.numel() * self.keys.element_size()
+        return (self.keys.numel() + self.values.numel()) * self.keys.element_size()
 
 
 class StateGroup:

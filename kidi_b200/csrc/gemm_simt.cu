@@ -16,7 +16,12 @@ constexpr int PAD = 4;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int M, int N, int K,
-                 long long ldx, long long ldw, long long ldy, const float* __restrict__ bias) {
+                 long long ldx, long long ldw, long long ldy, const float* __restrict__ bias, long long batch_x,
+                 long long batch_w, long long batch_y) {
+    // blockIdx.z: one product of a batch whose operands lie `batch_*` elements apart (0, 0, 0 without one)
+    x += blockIdx.z * batch_x;
+    w += blockIdx.z * batch_w;
+    y += blockIdx.z * batch_y;
     __shared__ float xs[TILE_K][TILE + PAD];
     __shared__ float ws[TILE_K][TILE + PAD];
     const int tx = threadIdx.x & 15;   // 4 output columns (n) each
@@ -67,10 +72,11 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
 
 template <typename TX, typename TW, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
-           const float* bias, cudaStream_t stream) {
-    dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE);
+           const float* bias, cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0,
+           long long batch_y = 0) {
+    dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE, batch);
     return kidi_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K,
-                       ldx, ldw, ldy, bias);
+                       ldx, ldw, ldy, bias, batch_x, batch_w, batch_y);
 }
 }  // namespace
 
@@ -91,6 +97,25 @@ KIDI_API int kidi_gemm_simt(const void* x, int x_dtype, const void* w, int w_dty
     KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, KIDI_BF16, bf16)
     KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_F32, float)
     KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_BF16, bf16)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+// The same for a batch of products (one per head, say): product b takes x + b * batch_x, w + b * batch_w and
+// writes y + b * batch_y (strides in elements). Each output is the same ascending-k chain as above.
+KIDI_API int kidi_gemm_simt_batched(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int M,
+                                    int N, int K, long long ldx, long long ldw, long long ldy, int batch,
+                                    long long batch_x, long long batch_w, long long batch_y, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || (M + TILE - 1) / TILE > 65535 || batch > 65535) return KIDI_REFUSED_SIZE;
+#define KIDI_CASE(X, TX, W, TW, Y, TY)                                 \
+    if (x_dtype == X && w_dtype == W && y_dtype == Y)                  \
+        return launch<TX, TW, TY>(x, w, y, M, N, K, ldx, ldw, ldy, nullptr, stream, batch, batch_x, batch_w, batch_y);
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, KIDI_BF16, bf16)
 #undef KIDI_CASE
     return KIDI_REFUSED_DTYPE;
 }

@@ -1,0 +1,273 @@
+// Row-wise kernels beside the RMSNorm of elementwise.cu: a layer norm with weight and bias on the
+// residual stream, an RMS norm of plain rows (whole rows or groups of a row, any element type), the
+// PolyNorm activation, the gate of a per-layer token input, its normalised addition to the stream, a
+// weighted sum of kept copies of the stream, and an add-and-cast of the stream.
+//
+// Everything that is summed over a row (means, variances, mean squares) is 32-bit; the residual stream
+// is 32-bit in every engine dtype. Each reduction's order depends on the row's width only, so a row's
+// result does not depend on what else the launch holds.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROW_THREADS = 256;
+
+// ---------------------------------------------------------------- residual add + layer norm
+// One block per output row r; source row s = row_index ? row_index[r] : r.
+//   v = residual[s] + delta[s] (delta optional); if write_residual: residual[s] = v
+//   y[r] = (v - mean(v)) / sqrt(mean((v - mean)^2) + eps) * w + b
+// The row is staged in shared memory; the variance is taken of the deviations (second pass).
+template <typename TD, typename TY>
+__global__ void __launch_bounds__(ROW_THREADS)
+add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ weight,
+                     const float* __restrict__ bias, TY* __restrict__ y, const int* __restrict__ row_index,
+                     int hidden, float eps, int write_residual) {
+    extern __shared__ float staged[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float* h = residual + s * hidden;
+    float sum = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+        float value = h[c];
+        if (delta) value += to_float(delta[s * hidden + c]);
+        if (write_residual) h[c] = value;
+        staged[c] = value;
+        sum += value;
+    }
+    const float mean = block_sum<ROW_THREADS>(sum, scratch) / (float)hidden;
+    float square = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+        const float deviation = staged[c] - mean;
+        square = fmaf(deviation, deviation, square);
+    }
+    const float variance = block_sum<ROW_THREADS>(square, scratch) / (float)hidden;
+    const float inv = 1.0f / sqrtf(variance + eps);
+    TY* out = y + (long long)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += ROW_THREADS)
+        out[c] = from_float<TY>((staged[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
+}
+
+// ---------------------------------------------------------------- RMS norm of groups of plain rows
+// One warp per (row, group): out[row, g*width + c] = x[row, g*width + c] / sqrt(mean_c(x^2) + eps) * w[c]
+// (w optional, shared by the groups).
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_rows_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ out, long long ldo,
+                const float* __restrict__ weight, int rows, int groups, int width, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)rows * groups) return;
+    const int row = (int)(item / groups), group = (int)(item - (long long)row * groups);
+    const T* source = x + row * ldx + (long long)group * width;
+    T* target = out + row * ldo + (long long)group * width;
+    float square = 0.f;
+    for (int c = lane; c < width; c += 32) {
+        const float value = to_float(source[c]);
+        square = fmaf(value, value, square);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(square) / (float)width + eps);
+    for (int c = lane; c < width; c += 32)
+        target[c] = from_float<T>(to_float(source[c]) * inv * (weight ? weight[c] : 1.f));
+}
+
+// ---------------------------------------------------------------- PolyNorm
+// out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e over a row of `width` values, powers
+// element by element, rms(u) = sqrt(mean(u^2) + eps).
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+poly_norm_kernel(const T* __restrict__ z, T* __restrict__ out, const float* __restrict__ coefficients, int width,
+                 float eps) {
+    __shared__ float scratch[32];
+    const long long row = blockIdx.x;
+    const T* source = z + row * width;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+        const float v = to_float(source[c]);
+        const float v2 = v * v, v3 = v2 * v;
+        s2 += v2;
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v3, v3, s6);
+    }
+    const float r1 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s2, scratch) / (float)width + eps);
+    const float r2 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s4, scratch) / (float)width + eps);
+    const float r3 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s6, scratch) / (float)width + eps);
+    const float a = coefficients[0] * r1, b = coefficients[1] * r2, c3 = coefficients[2] * r3, e = coefficients[3];
+    T* target = out + row * width;
+    for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+        const float v = to_float(source[c]);
+        const float v2 = v * v;
+        target[c] = from_float<T>(a * v + b * v2 + c3 * v2 * v + e);
+    }
+}
+
+// ---------------------------------------------------------------- gate of a per-layer token input
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// g[r, c] = gelu_tanh(gate[r, c]) * table[token[r], offset + c], c < dim.
+template <typename T, typename TW>
+__global__ void token_gate_kernel(const T* __restrict__ gate, T* __restrict__ out, const TW* __restrict__ table,
+                                  long long table_ld, int offset, const int* __restrict__ tokens, int vocab,
+                                  long long total, int dim) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / dim;
+    const int c = (int)(index - row * dim);
+    const int token = tokens[row];
+    const float e = token >= 0 && token < vocab ? to_float(table[token * table_ld + offset + c]) : 0.f;
+    out[index] = from_float<T>(gelu_tanh(to_float(gate[index])) * e);
+}
+
+// ---------------------------------------------------------------- normalised addition, weighted sum of kept streams
+// One block per row r:
+//   x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w                       (y may be null: nothing is added)
+//   if mixed: mixed[r] = sum_{j < count} mix[j] * kept[j][r]           kept[j] = kept + j * kept_stride
+// (x itself is usually the last of the kept streams: it is written before it is summed.)
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+add_normed_mix_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ weight, int hidden,
+                      float eps, const float* __restrict__ kept, long long kept_stride, const float* __restrict__ mix,
+                      int count, float* __restrict__ mixed) {
+    __shared__ float scratch[32];
+    const long long r = blockIdx.x;
+    float* row = x + r * hidden;
+    if (y) {
+        const T* addend = y + r * hidden;
+        float square = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+            const float v = to_float(addend[c]);
+            square = fmaf(v, v, square);
+        }
+        const float inv = 1.0f / sqrtf(block_sum<ROW_THREADS>(square, scratch) / (float)hidden + eps);
+        for (int c = threadIdx.x; c < hidden; c += ROW_THREADS)   // a thread reads below what it wrote itself
+            row[c] += to_float(addend[c]) * inv * weight[c];
+    }
+    if (!mixed) return;
+    for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+        float total = 0.f;
+        for (int j = 0; j < count; ++j) total = fmaf(mix[j], kept[j * kept_stride + r * hidden + c], total);
+        mixed[r * hidden + c] = total;
+    }
+}
+
+// x += delta (32-bit, in place; delta optional) and, if asked, a copy of x in T.
+template <typename TD, typename T>
+__global__ void add_cast_kernel(float* __restrict__ x, const TD* __restrict__ delta, T* __restrict__ copy,
+                                long long total) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    float value = x[index];
+    if (delta) {
+        value += to_float(delta[index]);
+        x[index] = value;
+    }
+    if (copy) copy[index] = from_float<T>(value);
+}
+
+}  // namespace
+
+KIDI_API int kidi_add_layernorm(float* residual, const void* delta, int delta_dtype, const float* weight,
+                                const float* bias, void* y, int y_dtype, const int* row_index, int rows, int hidden,
+                                float eps, int write_residual, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (delta_dtype == KIDI_NONE) { delta = nullptr; delta_dtype = KIDI_F32; }
+    const size_t shared = (size_t)hidden * sizeof(float);
+    if (hidden <= 0 || shared > 200 * 1024) return KIDI_REFUSED_SIZE;
+#define KIDI_CASE(D, TD, Y, TY)                                                                                    \
+    if (delta_dtype == D && y_dtype == Y) {                                                                        \
+        auto kernel = add_layernorm_kernel<TD, TY>;                                                                \
+        if (shared > 48 * 1024) {                                                                                  \
+            cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared); \
+            if (status != cudaSuccess) return (int)status;                                                         \
+        }                                                                                                          \
+        return kidi_launch(kernel, rows, ROW_THREADS, shared, stream, residual, (const TD*)delta, weight, bias,    \
+                           (TY*)y, row_index, hidden, eps, write_residual);                                        \
+    }
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_rms_rows(const void* x, long long ldx, void* out, long long ldo, int dtype, const float* weight,
+                           int rows, int groups, int width, float eps, cudaStream_t stream) {
+    if (rows <= 0 || groups <= 0) return 0;
+    if (width <= 0) return KIDI_REFUSED_SIZE;
+    const long long items = (long long)rows * groups;
+    if ((items + 3) / 4 > 0x7fffffffLL) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    if (dtype == KIDI_F32)
+        return kidi_launch(rms_rows_kernel<float>, blocks, 128, 0, stream, (const float*)x, ldx, (float*)out, ldo,
+                           weight, rows, groups, width, eps);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(rms_rows_kernel<bf16>, blocks, 128, 0, stream, (const bf16*)x, ldx, (bf16*)out, ldo, weight,
+                           rows, groups, width, eps);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_poly_norm(const void* z, void* out, int dtype, const float* coefficients, int rows, int width,
+                            float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return KIDI_REFUSED_SIZE;
+    if (dtype == KIDI_F32)
+        return kidi_launch(poly_norm_kernel<float>, rows, ROW_THREADS, 0, stream, (const float*)z, (float*)out,
+                           coefficients, width, eps);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(poly_norm_kernel<bf16>, rows, ROW_THREADS, 0, stream, (const bf16*)z, (bf16*)out,
+                           coefficients, width, eps);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_token_gate(const void* gate, void* out, int dtype, const void* table, int table_dtype,
+                             long long table_ld, int offset, const int* tokens, int vocab, int rows, int dim,
+                             cudaStream_t stream) {
+    const long long total = (long long)rows * dim;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+#define KIDI_CASE(D, T, W, TW)                                                                                 \
+    if (dtype == D && table_dtype == W)                                                                        \
+        return kidi_launch(token_gate_kernel<T, TW>, blocks, 256, 0, stream, (const T*)gate, (T*)out,          \
+                           (const TW*)table, table_ld, offset, tokens, vocab, total, dim);
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_add_normed_mix(float* x, const void* y, int y_dtype, const float* weight, int rows, int hidden,
+                                 float eps, const float* kept, long long kept_stride, const float* mix, int count,
+                                 float* mixed, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (mixed && (count <= 0 || !kept || !mix)) || (y && !weight)) return KIDI_REFUSED_SIZE;
+    if (y_dtype == KIDI_NONE) { y = nullptr; y_dtype = KIDI_F32; }
+    if (y_dtype == KIDI_F32)
+        return kidi_launch(add_normed_mix_kernel<float>, rows, ROW_THREADS, 0, stream, x, (const float*)y, weight,
+                           hidden, eps, kept, kept_stride, mix, count, mixed);
+    if (y_dtype == KIDI_BF16)
+        return kidi_launch(add_normed_mix_kernel<bf16>, rows, ROW_THREADS, 0, stream, x, (const bf16*)y, weight, hidden,
+                           eps, kept, kept_stride, mix, count, mixed);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_add_cast(float* x, const void* delta, int delta_dtype, void* copy, int copy_dtype, long long total,
+                           cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (delta_dtype == KIDI_NONE) { delta = nullptr; delta_dtype = KIDI_F32; }
+    if (copy_dtype == KIDI_NONE) { copy = nullptr; copy_dtype = KIDI_F32; }
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+#define KIDI_CASE(D, TD, C, T)                                                                                  \
+    if (delta_dtype == D && copy_dtype == C)                                                                    \
+        return kidi_launch(add_cast_kernel<TD, T>, blocks, 256, 0, stream, x, (const TD*)delta, (T*)copy, total);
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}

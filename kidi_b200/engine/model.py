@@ -24,6 +24,10 @@ from ..parts import embedding as _embedding  # noqa: F401
 from ..parts import feed_forward as _feed_forward  # noqa: F401
 from ..parts import norm as _norm  # noqa: F401
 from ..parts import position as _position  # noqa: F401
+from ..parts import gated_recurrence as _gated_recurrence  # noqa: F401
+from ..parts import latent_attention as _latent_attention  # noqa: F401
+from ..parts import stream_mix as _stream_mix  # noqa: F401
+from ..parts import token_input as _token_input  # noqa: F401
 
 
 class CausalLM:
@@ -34,6 +38,8 @@ class CausalLM:
         self.env = BuildEnv(dtype=dtype, device=torch.device(device), max_positions=spec.max_positions)
         for name, position in spec.positions.items():
             self.env.positions[name] = part_registry.build_part("position", position, self.env)
+        for name, shared in spec.shared.items():
+            self.env.shared[name] = part_registry.build_part("shared", shared, self.env)
         self.embedding = part_registry.build_part("embedding", spec.embedding, self.env)
         self.layers: List[Part] = []
         for layer in spec.layers:
@@ -43,6 +49,12 @@ class CausalLM:
             if missing:
                 raise invalid_argument(f"arrangement '{layer.arrangement.kind}' lacks parts: {', '.join(missing)}")
             parts = {role: part_registry.build_part(roles[role], layer.parts[role], self.env) for role in roles}
+            for role, kind in getattr(arrangement, "OPTIONAL_ROLES", {}).items():
+                if layer.parts.get(role) is not None:
+                    parts[role] = part_registry.build_part(kind, layer.parts[role], self.env)
+            unknown = [role for role in layer.parts if role not in parts and layer.parts[role] is not None]
+            if unknown:
+                raise invalid_argument(f"arrangement '{layer.arrangement.kind}' has no part '{unknown[0]}'")
             self.layers.append(arrangement(layer.arrangement, self.env, parts))
         self.final_norm = part_registry.build_part("norm", spec.final_norm, self.env)
         self.head = part_registry.build_part("head", spec.head, self.env)
@@ -56,7 +68,8 @@ class CausalLM:
 
     # ------------------------------------------------------------------ tensors
     def _top_parts(self) -> Sequence[Part]:
-        return [self.embedding, *self.env.positions.values(), *self.layers, self.final_norm, self.head]
+        return [self.embedding, *self.env.positions.values(), *self.env.shared.values(), *self.layers,
+                self.final_norm, self.head]
 
     def parameters(self) -> List[Tuple[str, ParamSpec]]:
         found: List[Tuple[str, ParamSpec]] = []

@@ -113,6 +113,22 @@ def core():
         lib.kidi_argmax_slices.restype = c_int
         lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p]
+        lib.kidi_add_layernorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                           c_int, c_int, c_float, c_int, c_void_p]
+        lib.kidi_rms_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
+                                      c_float, c_void_p]
+        lib.kidi_poly_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
+        lib.kidi_token_gate.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int,
+                                        c_int, c_int, c_void_p]
+        lib.kidi_add_normed_mix.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
+                                            c_longlong, c_void_p, c_int, c_void_p, c_void_p]
+        lib.kidi_add_cast.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
+        lib.kidi_gemm_simt_batched.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_longlong, c_longlong, c_longlong, c_int, c_longlong, c_longlong,
+                                               c_longlong, c_void_p]
+        for name in ("kidi_add_layernorm", "kidi_rms_rows", "kidi_poly_norm", "kidi_token_gate", "kidi_add_normed_mix",
+                     "kidi_add_cast", "kidi_gemm_simt_batched"):
+            getattr(lib, name).restype = c_int
         for name in ("kidi_embedding", "kidi_add_rmsnorm", "kidi_silu_gate", "kidi_gemm_simt", "kidi_add_bias",
                      "kidi_apply_row_factors", "kidi_rope_store",
                      "kidi_attention_generic", "kidi_argmax", "kidi_sample", "kidi_advance_decode"):
@@ -195,6 +211,135 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
         _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else NONE, _ptr(weight),
         dtype_code(weight.dtype), _ptr(out), dtype_code(out.dtype), _ptr(row_index), rows, hidden, float(eps),
         0 if row_index is not None else 1, _stream()), "add_rmsnorm")
+    return out
+
+
+def _float_vector(vector: Optional[torch.Tensor], size: int, what: str) -> None:
+    if vector is not None and (vector.dtype != torch.float32 or vector.shape != (size,) or not vector.is_contiguous()):
+        raise invalid_argument(f"{what} must be a contiguous float32 vector of {size} elements")
+
+
+def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                  bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += delta (in place, float32), then y = (v - mean) / sqrt(var + eps) * weight + bias over each
+    row v of the residual. With `row_index`, row r of the output comes from row row_index[r] and the
+    residual is left as it is."""
+    _need_cuda(residual, delta, weight, bias, row_index)
+    if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
+        raise invalid_argument("the residual stream is a contiguous float32 matrix")
+    hidden = residual.shape[1]
+    if delta is not None and (delta.shape != residual.shape or not delta.is_contiguous()):
+        raise invalid_argument("the residual delta must match the residual stream")
+    _float_vector(weight, hidden, "the norm weight")
+    _float_vector(bias, hidden, "the norm bias")
+    if row_index is not None and (row_index.dtype != torch.int32 or row_index.dim() != 1):
+        raise invalid_argument("row_index must be an int32 vector")
+    rows = row_index.shape[0] if row_index is not None else residual.shape[0]
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=residual.device)
+    _check(core().kidi_add_layernorm(
+        _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else NONE, _ptr(weight), _ptr(bias),
+        _ptr(out), dtype_code(out.dtype), _ptr(row_index), rows, hidden, float(eps),
+        0 if row_index is not None else 1, _stream()), "add_layernorm")
+    return out
+
+
+def rms_rows(x: torch.Tensor, width: int, weight: Optional[torch.Tensor], eps: float,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Every group of `width` consecutive entries of a row of x (the row holds a whole number of groups)
+    divided by its root mean square and multiplied by `weight` (float32 [width], shared by the groups)."""
+    _need_cuda(x, weight, out)
+    if x.dim() != 2 or x.stride(1) != 1 or width <= 0 or x.shape[1] % width:
+        raise invalid_argument("rms_rows takes rows that hold a whole number of groups")
+    _float_vector(weight, width, "the norm weight")
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    if out.shape != x.shape or out.dtype != x.dtype or out.stride(1) != 1:
+        raise invalid_argument("rms_rows: the output must match the input")
+    _check(core().kidi_rms_rows(_ptr(x), x.stride(0), _ptr(out), out.stride(0), dtype_code(x.dtype), _ptr(weight),
+                                x.shape[0], x.shape[1] // width, width, float(eps), _stream()), "rms_rows")
+    return out
+
+
+def poly_norm(z: torch.Tensor, coefficients: torch.Tensor, eps: float) -> torch.Tensor:
+    """a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e over each row, (a, b, c, e) = coefficients."""
+    _need_cuda(z, coefficients)
+    if z.dim() != 2 or not z.is_contiguous():
+        raise invalid_argument("poly_norm takes a contiguous matrix")
+    _float_vector(coefficients, 4, "the PolyNorm coefficients")
+    out = torch.empty_like(z)
+    _check(core().kidi_poly_norm(_ptr(z), _ptr(out), dtype_code(z.dtype), _ptr(coefficients), z.shape[0], z.shape[1],
+                                 float(eps), _stream()), "poly_norm")
+    return out
+
+
+def token_gate(gate: torch.Tensor, table: torch.Tensor, offset: int, tokens: torch.Tensor) -> torch.Tensor:
+    """gelu_tanh(gate[r, c]) * table[tokens[r], offset + c]."""
+    _need_cuda(gate, table, tokens)
+    rows, dim = gate.shape
+    if not gate.is_contiguous() or table.dim() != 2 or table.stride(1) != 1 or offset < 0 or offset + dim > table.shape[1]:
+        raise invalid_argument("token_gate: the gate must be contiguous and the table hold the asked columns")
+    if tokens.dtype != torch.int32 or tokens.shape[0] < rows:
+        raise invalid_argument("token_gate takes int32 token ids, one per row")
+    out = torch.empty_like(gate)
+    _check(core().kidi_token_gate(_ptr(gate), _ptr(out), dtype_code(gate.dtype), _ptr(table), dtype_code(table.dtype),
+                                  table.stride(0), int(offset), _ptr(tokens), table.shape[0], rows, dim, _stream()),
+           "token_gate")
+    return out
+
+
+def add_normed_mix(x: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                   kept: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                   mixed: Optional[torch.Tensor] = None) -> None:
+    """x += y / rms(y) * weight (x float32 in place; y optional), then, if `mixed` is given,
+    mixed = sum_j mix[j] * kept[j] over the first len(mix) matrices of `kept` [n, rows, hidden] (float32; x is
+    usually one of them)."""
+    _need_cuda(x, y, weight, kept, mix, mixed)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise invalid_argument("the residual stream is a contiguous float32 matrix")
+    rows, hidden = x.shape
+    if y is not None:
+        if y.shape != x.shape or not y.is_contiguous():
+            raise invalid_argument("add_normed_mix: y must match the stream")
+        _float_vector(weight, hidden, "the norm weight")
+    count = 0
+    if mixed is not None:
+        count = mix.shape[0]
+        if (kept.dtype != torch.float32 or kept.dim() != 3 or kept.shape[1:] != x.shape or not kept.is_contiguous()
+                or kept.shape[0] < count or mix.dtype != torch.float32 or not mix.is_contiguous()
+                or mixed.dtype != torch.float32 or mixed.shape != x.shape or not mixed.is_contiguous()):
+            raise invalid_argument("add_normed_mix: kept streams, weights and result must be float32 and fit the stream")
+    _check(core().kidi_add_normed_mix(_ptr(x), _ptr(y), dtype_code(y.dtype) if y is not None else NONE, _ptr(weight),
+                                      rows, hidden, float(eps), _ptr(kept), rows * hidden, _ptr(mix), count,
+                                      _ptr(mixed), _stream()), "add_normed_mix")
+
+
+def add_cast(x: torch.Tensor, delta: Optional[torch.Tensor], copy_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """x += delta (float32, in place) and a copy of x in `copy_dtype` (None: no copy)."""
+    _need_cuda(x, delta)
+    if x.dtype != torch.float32 or not x.is_contiguous() or (delta is not None and (delta.shape != x.shape or not delta.is_contiguous())):
+        raise invalid_argument("add_cast takes a contiguous float32 matrix and a delta of its shape")
+    copy = torch.empty(x.shape, dtype=copy_dtype, device=x.device) if copy_dtype is not None else None
+    _check(core().kidi_add_cast(_ptr(x), _ptr(delta), dtype_code(delta.dtype) if delta is not None else NONE,
+                                _ptr(copy), dtype_code(copy_dtype) if copy_dtype is not None else NONE, x.numel(),
+                                _stream()), "add_cast")
+    return copy
+
+
+def gemm_heads(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """A product per head: out[r, h, :] = x[r, h, :] @ weight[h].T for x [rows, heads, K], weight [heads, N, K]
+    and out [rows, heads, N] (views whose last axis is contiguous), each output one ascending-k chain of 32-bit
+    multiply-adds."""
+    _need_cuda(x, weight, out)
+    if x.dim() != 3 or weight.dim() != 3 or out.dim() != 3 or x.stride(2) != 1 or out.stride(2) != 1 or not weight.is_contiguous():
+        raise invalid_argument("gemm_heads takes [rows, heads, K], [heads, N, K] and [rows, heads, N]")
+    rows, heads, K = x.shape
+    N = weight.shape[1]
+    if weight.shape != (heads, N, K) or out.shape != (rows, heads, N):
+        raise invalid_argument("gemm_heads: the shapes do not fit")
+    _check(core().kidi_gemm_simt_batched(_ptr(x), dtype_code(x.dtype), _ptr(weight), dtype_code(weight.dtype), _ptr(out),
+                                         dtype_code(out.dtype), rows, N, K, x.stride(0), K, out.stride(0), heads,
+                                         x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
     return out
 
 

@@ -21,6 +21,7 @@ from __future__ import annotations
 
 from typing import Dict
 
+from ..errors import invalid_argument
 from .base import Part, ResidualSink, ResidualStream, plain_rows
 from .registry import register_part
 
@@ -48,17 +49,28 @@ def sink_for(part: Part, stream: ResidualStream, norm):
 
 @register_part("arrangement", "pre_norm")
 class PreNormBlock(Part):
-    ROLES = {"input_norm": "norm", "mixer": "mixer", "post_norm": "norm", "feed_forward": "feed_forward"}
+    """Optional parts: without `feed_forward` (and `post_norm`) the block has its first sublayer only;
+    `token_input` adds a function of the rows' token ids to the stream after the sublayers; `stream_mix`
+    then replaces the stream by a function of the streams that earlier layers left."""
+
+    ROLES = {"input_norm": "norm", "mixer": "mixer"}
+    OPTIONAL_ROLES = {"post_norm": "norm", "feed_forward": "feed_forward", "token_input": "token_input",
+                      "stream_mix": "stream_mix"}
 
     def __init__(self, spec, env, parts: Dict[str, Part]):
         super().__init__(spec, env)
         self.input_norm = parts["input_norm"]
         self.mixer = parts["mixer"]
-        self.post_norm = parts["post_norm"]
-        self.feed_forward = parts["feed_forward"]
+        self.post_norm = parts.get("post_norm")
+        self.feed_forward = parts.get("feed_forward")
+        self.token_input = parts.get("token_input")
+        self.stream_mix = parts.get("stream_mix")
+        if (self.post_norm is None) != (self.feed_forward is None):
+            raise invalid_argument("a pre-norm block has a feed-forward and the norm before it, or neither")
 
     def children(self):
-        return (self.input_norm, self.mixer, self.post_norm, self.feed_forward)
+        return tuple(part for part in (self.input_norm, self.mixer, self.post_norm, self.feed_forward,
+                                       self.token_input, self.stream_mix) if part is not None)
 
     def cache_requests(self) -> list:
         return self.mixer.cache_requests()
@@ -69,7 +81,17 @@ class PreNormBlock(Part):
         return self.input_norm
 
     def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool, next_norm=None) -> None:
+        if self.stream_mix is not None:
+            self.stream_mix.begin(stream, ctx)
+        if self.token_input is not None or self.stream_mix is not None:
+            next_norm = None          # the stream changes once more before the next layer's norm reads it
         stream.add(self.mixer.forward(normed_for(self.input_norm, stream, self.mixer), ctx, views, owns_cache,
                                       **sink_for(self.mixer, stream, self.post_norm)))
-        stream.add(self.feed_forward.forward(normed_for(self.post_norm, stream, self.feed_forward), ctx,
-                                             **sink_for(self.feed_forward, stream, next_norm if FOLD_NORMS == "all" else None)))
+        if self.feed_forward is not None:
+            stream.add(self.feed_forward.forward(normed_for(self.post_norm, stream, self.feed_forward), ctx,
+                                                 **sink_for(self.feed_forward, stream,
+                                                            next_norm if FOLD_NORMS == "all" else None)))
+        if self.token_input is not None:
+            self.token_input.forward(stream, ctx, mix=self.stream_mix)
+        elif self.stream_mix is not None:
+            self.stream_mix.forward(stream, ctx)

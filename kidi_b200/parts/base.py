@@ -13,6 +13,11 @@ Interfaces by role (each is registered with `register_part(role, kind)`):
                  `takes_sink = True`: `forward(..., sink=ResidualSink)` may return None after adding y
                  to the residual stream itself)
 * arrangement:   `__init__(spec, env, parts)`; `forward(stream, ctx, views, owns_cache)`
+* token_input:   `forward(stream, ctx, mix=None)`: adds something computed from the rows' token ids to the stream
+                 (after taking the pending delta); `mix`, a stream_mix part, may be applied in the same kernel
+* stream_mix:    `begin(stream, ctx)` before a layer, `forward(stream, ctx)` after it: replaces the stream by a
+                 function of the copies of it that earlier layers left (`ResidualStream.kept`)
+* shared:        built once per model under a name (`ModelSpec.shared`); parts look it up in `env.shared`
 * embedding:     `forward(tokens, ctx) -> float32 [rows, hidden]`
 * head:          `forward(x, ctx) -> float32 [rows, vocab]`
 
@@ -37,6 +42,7 @@ class BuildEnv:
     device: torch.device
     max_positions: int
     positions: Dict[str, object] = dataclasses.field(default_factory=dict)
+    shared: Dict[str, object] = dataclasses.field(default_factory=dict)   # `ModelSpec.shared`, by name
 
 
 class Part:
@@ -152,6 +158,10 @@ class ResidualStream:
         self.hidden = hidden
         self.pending: Optional[torch.Tensor] = None
         self.prepared = None
+        # Copies of the stream that a part keeps for later layers (role "stream_mix"): [n, rows, hidden]
+        # float32, and how many of them are filled. `hidden` is then a view of one of them.
+        self.kept: Optional[torch.Tensor] = None
+        self.kept_count = 0
 
     def add(self, delta: Optional[torch.Tensor]) -> None:
         """`delta` None: the part that made it has added it through a sink already."""

@@ -27,13 +27,14 @@ class TokenEmbedding(Part):
         self.vocab = int(spec.param("vocab_size"))
         self.hidden = int(spec.param("hidden_size"))
         self.scale = float(spec.param("scale", 1.0))
+        self.name = spec.param("name", "weight")       # the table's tensor name under the prefix
         self.weight: Optional[torch.Tensor] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.vocab, self.hidden))]
+        return [ParamSpec(self.name, (self.vocab, self.hidden))]
 
     def bind(self, tensors) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.name]
 
     def forward(self, tokens: torch.Tensor, ctx) -> torch.Tensor:
         return ops.embedding(tokens, self.weight, self.scale)
@@ -46,13 +47,14 @@ class LinearHead(Part):
         self.vocab = int(spec.param("vocab_size"))
         self.hidden = int(spec.param("hidden_size"))
         self.tied_to = spec.param("tied_to", None)
+        self.name = spec.param("name", "weight")
         self.linear: Optional[Linear] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.vocab, self.hidden), alias_of=self.tied_to)]
+        return [ParamSpec(self.name, (self.vocab, self.hidden), alias_of=self.tied_to)]
 
     def bind(self, tensors) -> None:
-        self.linear = Linear(tensors["weight"])
+        self.linear = Linear(tensors[self.name])
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         return self.linear.forward(x, out_dtype=torch.float32)

@@ -63,3 +63,45 @@ class GatedFeedForward(Part):
         else:
             gated = ops.silu_gate(self.gate_up.forward(x))
         return self.down.forward(gated, sink=sink)
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseFeedForward(Part):
+    """y = act(x Wu^T) Wd^T with one up and one down projection and no gate. Parameters: hidden_size,
+    intermediate_size, activation, eps (of the activation's norms), up_name, down_name, act_name (tensor names
+    under the prefix). Activations:
+
+    * "poly_norm": a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(u) = u / sqrt(mean(u^2) + eps)
+      over the intermediate values of a token, and (a, b, c, e) a tensor of four numbers."""
+
+    ACTIVATIONS = ("poly_norm",)
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.inter = int(spec.param("intermediate_size"))
+        self.activation = spec.param("activation")
+        if self.activation not in self.ACTIVATIONS:
+            raise unsupported(f"dense feed-forward activation '{self.activation}' is not built "
+                              f"({', '.join(self.ACTIVATIONS)} are)")
+        self.eps = float(spec.param("eps", 1e-6))
+        self.up_name = spec.param("up_name", "up_proj.weight")
+        self.down_name = spec.param("down_name", "down_proj.weight")
+        self.act_name = spec.param("act_name", "act")
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.coefficients: Optional[torch.Tensor] = None
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.up_name, (self.inter, self.hidden)),
+                ParamSpec(self.down_name, (self.hidden, self.inter)),
+                ParamSpec(self.act_name, (4,), init=("normal", 0.5))]
+
+    def bind(self, tensors) -> None:
+        self.up = Linear(tensors[self.up_name])
+        self.down = Linear(tensors[self.down_name])
+        self.coefficients = tensors[self.act_name].float().contiguous()
+
+    def forward(self, x, ctx, sink=None) -> Optional[torch.Tensor]:
+        z = self.up.forward(x)
+        return self.down.forward(ops.poly_norm(z, self.coefficients, self.eps))

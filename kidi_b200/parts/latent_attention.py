@@ -1,0 +1,129 @@
+"""Attention whose keys and values are linear maps of a cached latent, as a mixer.
+
+A token leaves one row in the cache: its latent c = RMSNorm(first `kv_rank` rows of W_dkv h) and, from the last
+`rot_dim` rows of W_dkv h, one rotated key part that all heads share. Queries pass a latent of their own,
+c_q = RMSNorm(W_dq h), q = W_uq c_q, laid out per head as [dim plain | rot_dim rotated]. Head i's plain key is
+W_uk[i] c, its value W_uv[i] c; a score is (q_plain . k_plain + q_rot . k_rot) * scale, the softmax is causal
+(key u is visible from position p when u <= p and, with a window W, u > p - W), and W_o maps the concatenated
+heads back. The rotation pairs entries 2i and 2i+1 of the rotated part (the named position encoding gives the
+angles).
+
+The key map is folded into the query (q_lat = W_uk[i]^T q_plain, per head) and the value map is applied to the
+weighted sum of latents, so attention reads the cached rows only: it never materialises per-head keys or values.
+
+A layer with `kv_from` set has no W_dkv and reads the cache of the layer that is named as its cache source in
+the schedule; its own W_uk, W_uv, queries and mask apply.
+
+Parameters (`spec.params`): hidden_size, num_heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, eps, position
+(name of a rotary encoding of head width rot_dim), window (tokens or None), owns_latent (False: no W_dkv), and
+the tensor names under the prefix: dq, dq_norm, uq, dkv, dkv_norm, uk, uv, o.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..cache.sequence_cache import KVRequest
+from ..errors import invalid_argument, unsupported
+from ..kernels import latent as latent_kernels
+from ..kernels import ops
+from .base import Part, plain_rows
+from .linear import Linear
+from .registry import register_part
+from .spec import ParamSpec
+
+NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+         "o": "o"}
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.heads = int(spec.param("num_heads"))
+        self.dim = int(spec.param("dim"))
+        self.rot_dim = int(spec.param("rot_dim"))
+        self.vdim = int(spec.param("vdim"))
+        self.q_rank = int(spec.param("q_rank"))
+        self.rank = int(spec.param("kv_rank"))
+        self.scale = float(spec.param("scale"))
+        self.eps = float(spec.param("eps"))
+        self.window = spec.param("window", None)
+        self.owns_latent = bool(spec.param("owns_latent", True))
+        if min(self.hidden, self.heads, self.vdim, self.q_rank, self.rank, self.rot_dim) <= 0 or self.dim < 0:
+            raise invalid_argument("invalid latent attention dimensions")
+        if self.rank + self.rot_dim > 640:
+            raise unsupported(f"a cached row of {self.rank + self.rot_dim} values exceeds 640, the widest the kernels take")
+        if self.window is not None and int(self.window) <= 0:
+            raise invalid_argument("an attention window must be positive")
+        name = spec.param("position", None)
+        self.position = env.positions[name] if name is not None else None
+        if self.position is None:
+            raise invalid_argument("the rotated key part needs a position encoding")
+        if self.position.head_dim != self.rot_dim:
+            raise invalid_argument("the rotary encoding was built for another width of the rotated part")
+        self.names = {key: spec.param(key + "_name", default) for key, default in NAMES.items()}
+        self.dq = self.uq = self.dkv = self.out = None
+        self.dq_norm = self.dkv_norm = self.uk_folded = self.uv = None
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        n, head_q = self.names, self.dim + self.rot_dim
+        specs = [
+            ParamSpec(n["dq"], (self.q_rank, self.hidden)),
+            ParamSpec(n["dq_norm"], (self.q_rank,), init=("one_plus_normal", 0.1)),
+            ParamSpec(n["uq"], (self.heads * head_q, self.q_rank), init=("normal", 0.1)),
+            ParamSpec(n["uk"], (self.heads * self.dim, self.rank), init=("normal", 0.1)),
+            ParamSpec(n["uv"], (self.heads * self.vdim, self.rank), init=("normal", 0.1)),
+            ParamSpec(n["o"], (self.hidden, self.heads * self.vdim)),
+        ]
+        if self.owns_latent:
+            specs.append(ParamSpec(n["dkv"], (self.rank + self.rot_dim, self.hidden)))
+            specs.append(ParamSpec(n["dkv_norm"], (self.rank,), init=("one_plus_normal", 0.1)))
+        return specs
+
+    def bind(self, tensors) -> None:
+        n = self.names
+        self.dq, self.uq, self.out = Linear(tensors[n["dq"]]), Linear(tensors[n["uq"]]), Linear(tensors[n["o"]])
+        self.dq_norm = tensors[n["dq_norm"]].float().contiguous()
+        # W_uk per head, transposed: [heads, rank, dim], so that q_lat = q_plain @ W_uk[h] is a product with a
+        # weight stored [out, in] like every other.
+        self.uk_folded = tensors[n["uk"]].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.uv = tensors[n["uv"]].view(self.heads, self.vdim, self.rank).contiguous()
+        if self.owns_latent:
+            self.dkv = Linear(tensors[n["dkv"]])
+            self.dkv_norm = tensors[n["dkv_norm"]].float().contiguous()
+
+    def cache_requests(self) -> list:
+        # One row [c | rotated key part] per token and no values of their own: the values are maps of c.
+        return [KVRequest(1, self.rank + self.rot_dim, int(self.window) if self.window is not None else None,
+                          value_dim=0)]
+
+    def forward(self, x, ctx, views, owns_cache: bool, sink=None) -> Optional[torch.Tensor]:
+        x = plain_rows(x)
+        view = views[0]
+        if owns_cache != self.owns_latent:
+            raise invalid_argument("a latent attention layer either owns its latent and its cache, or neither")
+        if view.ring_pages > 0 and not ctx.plan.is_decode:
+            raise unsupported("latent attention over a windowed (ring) cache takes one token per step")
+        rows = x.shape[0]
+        heads, rank, rot_dim = self.heads, self.rank, self.rot_dim
+        q = self.uq.forward(ops.rms_rows(self.dq.forward(x), self.q_rank, self.dq_norm, self.eps))
+        kv = self.dkv.forward(x) if self.owns_latent else None
+        folded = torch.empty((rows, heads * (rank + rot_dim)), dtype=q.dtype, device=q.device)
+        position = self.position
+        latent_kernels.prepare(q, folded, kv, self.dkv_norm, heads=heads, dim=self.dim, rot_dim=rot_dim, rank=rank,
+                               rotary_dims=position.rotary_dim,
+                               cos=position.cos, sin=position.sin, eps=self.eps, tables=ctx.tables, kv_view=view)
+        if self.dim:
+            ops.gemm_heads(q.view(rows, heads, self.dim + rot_dim)[:, :, :self.dim], self.uk_folded,
+                           folded.view(rows, heads, rank + rot_dim)[:, :, :rank])
+        else:
+            folded.view(rows, heads, rank + rot_dim)[:, :, :rank].zero_()
+        summed = torch.empty((rows, heads * rank), dtype=q.dtype, device=q.device)
+        latent_kernels.attention(folded, summed, heads=heads, rank=rank, rot_dim=rot_dim, scale=self.scale,
+                                 window=self.window, tables=ctx.tables, kv_view=view)
+        attended = torch.empty((rows, heads * self.vdim), dtype=q.dtype, device=q.device)
+        ops.gemm_heads(summed.view(rows, heads, rank), self.uv, attended.view(rows, heads, self.vdim))
+        return self.out.forward(attended)

@@ -48,3 +48,31 @@ class RMSNorm(Part):
             return ready if scaled else ready.plain()
         return ops.add_rmsnorm(stream.hidden, stream.take_pending(), self.weight, self.eps, self.env.dtype,
                                row_index=rows)
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Part):
+    """y = (x - mean(x)) / sqrt(mean((x - mean)^2) + eps) * w + b over each row, in 32-bit, in the kernel
+    that also forms the residual sum. Parameters: size, eps, weight_name and bias_name (tensor names under
+    the prefix; default "weight" and "bias")."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size = int(spec.param("size"))
+        self.eps = float(spec.param("eps"))
+        self.weight_name = spec.param("weight_name", "weight")
+        self.bias_name = spec.param("bias_name", "bias")
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.weight_name, (self.size,), init=("one_plus_normal", 0.1)),
+                ParamSpec(self.bias_name, (self.size,), init=("normal", 0.1))]
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors[self.weight_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous()
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False):
+        return ops.add_layernorm(stream.hidden, stream.take_pending(), self.weight, self.bias, self.eps,
+                                 self.env.dtype, row_index=rows)

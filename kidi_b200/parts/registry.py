@@ -1,7 +1,7 @@
 """Registries of parts by role and kind.
 
 A part is registered under a role ("mixer", "feed_forward", "norm", "position",
-"arrangement", "embedding", "head") and a kind (any string). `build_part` makes
+"arrangement", "embedding", "head", "token_input", "stream_mix", "shared") and a kind (any string). `build_part` makes
 one from a `PartSpec`. A test or a user can register a part of its own and name it
 in a `ModelSpec` without touching this package.
 """
@@ -12,7 +12,8 @@ from typing import Callable, Dict
 from ..errors import unsupported
 from .spec import PartSpec
 
-ROLES = ("mixer", "feed_forward", "norm", "position", "arrangement", "embedding", "head")
+ROLES = ("mixer", "feed_forward", "norm", "position", "arrangement", "embedding", "head", "token_input", "stream_mix",
+         "shared")
 
 _PARTS: Dict[str, Dict[str, type]] = {role: {} for role in ROLES}
 

@@ -64,6 +64,8 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     eos_token_ids: Tuple[int, ...] = ()
+    shared: Mapping[str, PartSpec] = dataclasses.field(default_factory=dict)  # named parts (role "shared") built once
+                                                                               # that several layers read
     ignored_tensors: Tuple[str, ...] = ()  # regular expressions of tensor names a file may carry unused
 
 
@@ -135,8 +137,8 @@ class ParamSpec:
     parameter). `sources`, if given, is shorthand for the first such rule: (name, shape)
     pairs concatenated on axis 0 in order, which is the reference's q/k/v -> qkv and
     gate/up -> gate_up rule (src/kidi/model/qwen3.cpp:113-132).
-    `init` names the random-weights distribution: ("normal", std) or
-    ("one_plus_normal", std). `storage` is "float" (bfloat16, or 32-bit when the
+    `init` names the random-weights distribution: ("normal", std), ("one_plus_normal", std),
+    ("uniform", high) on [0, high) or ("last_one", std): N(0, std) with 1 added to the last entry. `storage` is "float" (bfloat16, or 32-bit when the
     file stores 32-bit) or "int32".
     """
 

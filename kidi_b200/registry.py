@@ -5,7 +5,8 @@ finds a model by the normalised `model_type` (src/kidi/model/registry.cpp:29-95;
 unknown types are UNSUPPORTED, src/kidi/checkpoint/config.cpp:260-264). Here an
 architecture registers a typed configuration class and a function that turns a
 configuration into a `ModelSpec`; config.json selects it through
-`architectures[0]`, or through `model_type` when that key is absent.
+`architectures[0]`, through `architecture` (one name), or through `model_type` when
+those keys are absent.
 """
 from __future__ import annotations
 
@@ -47,6 +48,8 @@ def registered_architectures() -> Tuple[str, ...]:
 
 def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
     """Chooses the architecture a config.json names."""
+    if not isinstance(config, Mapping):
+        raise invalid_manifest("config.json must hold a JSON object")
     _load_builtin()
     names = config.get("architectures")
     key = None
@@ -54,6 +57,10 @@ def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
         key = names[0]
     elif names is not None:
         raise invalid_manifest("'architectures' must be a non-empty list of strings")
+    elif config.get("architecture") is not None:
+        key = config["architecture"]
+        if not isinstance(key, str):
+            raise invalid_manifest("'architecture' must be a string")
     if key is None or key not in _ARCHITECTURES:
         model_type = config.get("model_type")
         if model_type is not None and not isinstance(model_type, str):
@@ -83,3 +90,4 @@ def _load_builtin() -> None:
     if not _LOADED:
         _LOADED = True
         from .models import qwen3  # noqa: F401  (registers itself)
+        from .models import sanozen  # noqa: F401

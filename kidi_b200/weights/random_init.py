@@ -39,6 +39,11 @@ def _draw(name: str, shape: Tuple[int, ...], init: Tuple[str, float], seed: int,
         values.mul_(std)
     elif kind == "one_plus_normal":
         values.mul_(std).add_(1.0)
+    elif kind == "uniform":
+        values = torch.rand(shape, generator=generator, dtype=torch.float32, device=device) * std
+    elif kind == "last_one":
+        values.mul_(std)
+        values.reshape(-1)[-1] += 1.0
     else:
         raise invalid_argument(f"unknown initialiser '{kind}' for tensor '{name}'")
     return values.to(dtype)
