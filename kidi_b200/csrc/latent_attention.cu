@@ -16,8 +16,10 @@ struct LatentPrepareArgs {
     long long ldq;
     void* folded;           // [rows, ldf]: per head [rank (filled by the caller) | rot_dim rotated, written here]
     long long ldf;
-    const void* kv;         // [rows, ldkv]: [rank latent | rot_dim shared key part], or null (nothing is cached)
+    void* kv;               // [rows, ldkv]: [rank latent | rot_dim shared key part], or null (nothing is cached)
     long long ldkv;
+    int write_back;         // the normalised latent and the rotated key part also replace the row of kv
+    int skip_queries;       // only the cache entries are made
     const float* kv_norm;   // [rank]
     const float* cos_table; // [positions, rotary_dims / 2]
     const float* sin_table;
@@ -34,7 +36,8 @@ struct LatentPrepareArgs {
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int units = a.heads + (a.kv ? 1 : 0);
+    const int heads = a.skip_queries ? 0 : a.heads;
+    const int units = heads + (a.kv ? 1 : 0);
     const long long item = (long long)blockIdx.x * 4 + warp;
     if (item >= (long long)a.rows * units) return;
     const int row = (int)(item / units), unit = (int)(item - (long long)row * units);
@@ -46,11 +49,12 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs a
     const float* sine = a.sin_table + (long long)position * half;
     const T* source;
     T* target;
-    if (unit < a.heads) {
+    T* second = nullptr;    // the row of kv, when it is written back
+    if (unit < heads) {
         source = (const T*)a.q + row * a.ldq + (long long)unit * (a.dim + a.rot_dim) + a.dim;
         target = (T*)a.folded + row * a.ldf + (long long)unit * (a.rank + a.rot_dim) + a.rank;
     } else {
-        const T* latent = (const T*)a.kv + row * a.ldkv;
+        T* latent = (T*)a.kv + row * a.ldkv;
         T* cached = (T*)a.cache + cache_row_offset(a.geometry, a.seq_slot[seq], position, 0);
         float square = 0.f;
         for (int c = lane; c < a.rank; c += 32) {
@@ -58,16 +62,23 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs a
             square = fmaf(value, value, square);
         }
         const float inv = 1.0f / sqrtf(warp_sum(square) / (float)a.rank + a.eps);
-        for (int c = lane; c < a.rank; c += 32) cached[c] = from_float<T>(to_float(latent[c]) * inv * a.kv_norm[c]);
+        for (int c = lane; c < a.rank; c += 32) {
+            const T normed = from_float<T>(to_float(latent[c]) * inv * a.kv_norm[c]);
+            cached[c] = normed;
+            if (a.write_back) latent[c] = normed;
+        }
         source = latent + a.rank;
         target = cached + a.rank;
+        if (a.write_back) second = latent + a.rank;
     }
     // entries 2i and 2i+1 turn by the angle of pair i; entries from rotary_dims on pass unchanged
     for (int i = lane; i < half; i += 32) {
         const float u = to_float(source[2 * i]), v = to_float(source[2 * i + 1]);
         const float c = cosine[i], s = sine[i];
-        target[2 * i] = from_float<T>(u * c - v * s);
-        target[2 * i + 1] = from_float<T>(v * c + u * s);
+        const T first = from_float<T>(u * c - v * s), other = from_float<T>(v * c + u * s);
+        target[2 * i] = first;
+        target[2 * i + 1] = other;
+        if (second) { second[2 * i] = first; second[2 * i + 1] = other; }   // the lane's own pair: read above
     }
     for (int c = a.rotary_dims + lane; c < a.rot_dim; c += 32) target[c] = source[c];
 }
@@ -75,10 +86,11 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs a
 KIDI_API int kidi_latent_prepare(const LatentPrepareArgs* args, int dtype, cudaStream_t stream) {
     const LatentPrepareArgs& a = *args;
     if (a.rows <= 0) return 0;
+    if (a.skip_queries && !a.kv) return 0;
     if (a.heads <= 0 || a.dim < 0 || a.rot_dim < 0 || a.rank <= 0 || a.rotary_dims < 0 || (a.rotary_dims & 1) ||
         a.rotary_dims > a.rot_dim)
         return KIDI_REFUSED_SIZE;
-    const long long items = (long long)a.rows * (a.heads + (a.kv ? 1 : 0));
+    const long long items = (long long)a.rows * ((a.skip_queries ? 0 : a.heads) + (a.kv ? 1 : 0));
     if ((items + 3) / 4 > 0x7fffffffLL) return KIDI_REFUSED_SIZE;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     if (dtype == KIDI_F32) return kidi_launch(latent_prepare_kernel<float>, blocks, 128, 0, stream, a);
@@ -185,5 +197,100 @@ KIDI_API int kidi_latent_attention(const LatentAttentionArgs* args, int dtype, c
     if (a.heads <= 0 || a.heads > 65535 || a.rank <= 0 || a.rot_dim < 0) return KIDI_REFUSED_SIZE;
     if (dtype == KIDI_F32) return launch_latent_attention<float>(a, stream);
     if (dtype == KIDI_BF16) return launch_latent_attention<bf16>(a, stream);
+    return KIDI_REFUSED_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// The unfolded form for prompts: every head's keys and values are computed from the latents of the step's rows
+// and packed, with the queries, into the matrix [rows, 3 * heads * D] (D = dim + rot_dim) that the prompt
+// attention kernels of grouped-query attention take: heads of [q_plain | q_rot turned], then heads of
+// [k_plain | shared rotated key part], then heads of [value | zeros up to D].
+struct LatentPackArgs {
+    const void* q;          // [rows, ldq]: per head [dim | rot_dim not yet turned]
+    long long ldq;
+    const void* latent;     // [rows, ldl]: [rank normalised | rot_dim turned] (as the cache holds them)
+    long long ldl;
+    const void* unfolded;   // [rows, ldu]: heads*dim plain keys, then heads*vdim values
+    long long ldu;
+    void* packed;           // [rows, ldp]
+    long long ldp;
+    const float* cos_table;
+    const float* sin_table;
+    const int* row_seq;
+    const int* row_pos;
+    int rows, heads, dim, rot_dim, rotary_dims, rank, vdim;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) latent_pack_kernel(LatentPackArgs a) {
+    const int row = blockIdx.x;
+    const int D = a.dim + a.rot_dim, half = a.rotary_dims / 2;
+    const int position = a.row_seq[row] < 0 ? 0 : a.row_pos[row];
+    const float* cosine = a.cos_table + (long long)position * half;
+    const float* sine = a.sin_table + (long long)position * half;
+    const T* q = (const T*)a.q + row * a.ldq;
+    const T* latent = (const T*)a.latent + row * a.ldl;
+    const T* unfolded = (const T*)a.unfolded + row * a.ldu;
+    T* packed = (T*)a.packed + row * a.ldp;
+    const int per_section = a.heads * D;
+    for (int index = threadIdx.x; index < 3 * per_section; index += 128) {
+        const int section = index / per_section, within = index - section * per_section;
+        const int head = within / D, c = within - head * D;
+        T value;
+        if (section == 0) {
+            const T* source = q + head * D;
+            if (c < a.dim || c >= a.dim + a.rotary_dims) {
+                value = source[c];
+            } else {
+                const int j = c - a.dim, i = j >> 1;
+                const float u = to_float(source[a.dim + 2 * i]), v = to_float(source[a.dim + 2 * i + 1]);
+                value = from_float<T>((j & 1) ? v * cosine[i] + u * sine[i] : u * cosine[i] - v * sine[i]);
+            }
+        } else if (section == 1) {
+            value = c < a.dim ? unfolded[head * a.dim + c] : latent[a.rank + c - a.dim];
+        } else {
+            value = c < a.vdim ? unfolded[a.heads * a.dim + head * a.vdim + c] : from_float<T>(0.f);
+        }
+        packed[index] = value;
+    }
+}
+
+KIDI_API int kidi_latent_pack(const LatentPackArgs* args, int dtype, cudaStream_t stream) {
+    const LatentPackArgs& a = *args;
+    if (a.rows <= 0) return 0;
+    if (a.heads <= 0 || a.vdim > a.dim + a.rot_dim || a.rotary_dims > a.rot_dim || (a.rotary_dims & 1)) return KIDI_REFUSED_SIZE;
+    if (dtype == KIDI_F32) return kidi_launch(latent_pack_kernel<float>, a.rows, 128, 0, stream, a);
+    if (dtype == KIDI_BF16) return kidi_launch(latent_pack_kernel<bf16>, a.rows, 128, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
+}
+
+// Rows of the step as the cache holds them: out[r] = the cached entry of row r's sequence at row r's position
+// (for a layer that reads another layer's cached rows). Padding rows get zeros.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_gather_kernel(const T* __restrict__ cache, CacheGeometry geometry, T* __restrict__ out, long long ldo,
+                     const int* __restrict__ row_seq, const int* __restrict__ row_pos, const int* __restrict__ seq_slot,
+                     int width) {
+    const int row = blockIdx.x;
+    const int seq = row_seq[row];
+    T* target = out + row * ldo;
+    if (seq < 0) {
+        for (int c = threadIdx.x; c < width; c += 128) target[c] = from_float<T>(0.f);
+        return;
+    }
+    const T* entry = cache + cache_row_offset(geometry, seq_slot[seq], row_pos[row], 0);
+    for (int c = threadIdx.x; c < width; c += 128) target[c] = entry[c];
+}
+
+KIDI_API int kidi_latent_gather(const void* cache, const CacheGeometry* geometry, void* out, long long ldo,
+                                const int* row_seq, const int* row_pos, const int* seq_slot, int rows, int width,
+                                int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == KIDI_F32)
+        return kidi_launch(latent_gather_kernel<float>, rows, 128, 0, stream, (const float*)cache, *geometry,
+                           (float*)out, ldo, row_seq, row_pos, seq_slot, width);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(latent_gather_kernel<bf16>, rows, 128, 0, stream, (const bf16*)cache, *geometry, (bf16*)out,
+                           ldo, row_seq, row_pos, seq_slot, width);
     return KIDI_REFUSED_DTYPE;
 }

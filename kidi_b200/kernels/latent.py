@@ -19,7 +19,7 @@ from .ops import CacheGeometry, _check, c_float, c_int, c_longlong, c_void_p, ca
 
 class PrepareArgs(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("ldq", c_longlong), ("folded", c_void_p), ("ldf", c_longlong), ("kv", c_void_p),
-                ("ldkv", c_longlong), ("kv_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p),
+                ("ldkv", c_longlong), ("write_back", c_int), ("skip_queries", c_int), ("kv_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p),
                 ("row_seq", c_void_p), ("row_pos", c_void_p), ("seq_slot", c_void_p), ("cache", c_void_p),
                 ("geometry", CacheGeometry), ("rows", c_int), ("heads", c_int), ("dim", c_int), ("rot_dim", c_int),
                 ("rotary_dims", c_int), ("rank", c_int), ("eps", c_float)]
@@ -41,23 +41,30 @@ def library():
         lib = load_library("latent_attention")
         lib.kidi_latent_prepare.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_latent_attention.argtypes = [c_void_p, c_int, c_void_p]
-        lib.kidi_latent_prepare.restype = lib.kidi_latent_attention.restype = c_int
+        lib.kidi_latent_pack.argtypes = [c_void_p, c_int, c_void_p]
+        lib.kidi_latent_gather.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_int, c_int, c_void_p]
+        for name in ("kidi_latent_prepare", "kidi_latent_attention", "kidi_latent_pack", "kidi_latent_gather"):
+            getattr(lib, name).restype = c_int
         _library = lib
     return _library
 
 
-def prepare(q: torch.Tensor, folded: torch.Tensor, kv: Optional[torch.Tensor], kv_norm: Optional[torch.Tensor], *,
+def prepare(q: torch.Tensor, folded: Optional[torch.Tensor], kv: Optional[torch.Tensor], kv_norm: Optional[torch.Tensor], *,
             heads: int, dim: int, rot_dim: int, rank: int, rotary_dims: int, cos: torch.Tensor, sin: torch.Tensor,
-            eps: float, tables, kv_view) -> None:
-    """q [rows, heads * (dim + rot_dim)]: the rotated part of every head is turned by its row's position and
+            eps: float, tables, kv_view, write_back: bool = False) -> None:
+    """Without `folded` only the cache entries are made; with `write_back` the normalised latent and the rotated
+    key part also replace the rows of kv. q [rows, heads * (dim + rot_dim)]: the rotated part of every head is turned by its row's position and
     written to folded[:, head, rank:] (folded [rows, heads * (rank + rot_dim)]). kv [rows, rank + rot_dim], if
     given: its first `rank` entries, RMS-normalised with `kv_norm`, and its rotated last rot_dim entries become
     the row's cache entry."""
     ops._need_cuda(q, folded, kv, kv_norm, cos, sin)
     rows = q.shape[0]
-    if q.shape != (rows, heads * (dim + rot_dim)) or folded.shape != (rows, heads * (rank + rot_dim)) \
-            or q.stride(1) != 1 or folded.stride(1) != 1 or folded.dtype != q.dtype:
-        raise invalid_argument("latent prepare: queries or folded queries have the wrong shape")
+    if q.shape != (rows, heads * (dim + rot_dim)) or q.stride(1) != 1:
+        raise invalid_argument("latent prepare: the queries have the wrong shape")
+    if folded is not None and (folded.shape != (rows, heads * (rank + rot_dim)) or folded.stride(1) != 1
+                               or folded.dtype != q.dtype):
+        raise invalid_argument("latent prepare: the folded queries have the wrong shape")
     if cos.dtype != torch.float32 or cos.dim() != 2 or cos.shape[1] != rotary_dims // 2 or sin.shape != cos.shape:
         raise invalid_argument("latent prepare: the rotation tables must be float32 [positions, rotary_dims/2]")
     if kv is not None:
@@ -68,8 +75,9 @@ def prepare(q: torch.Tensor, folded: torch.Tensor, kv: Optional[torch.Tensor], k
         if kv_view is None or kv_view.keys.dtype != q.dtype or kv_view.keys.shape[-1] != rank + rot_dim:
             raise invalid_argument("latent prepare: the cache does not fit the latent rows")
     args = PrepareArgs(
-        q.data_ptr(), q.stride(0), folded.data_ptr(), folded.stride(0), kv.data_ptr() if kv is not None else 0,
-        kv.stride(0) if kv is not None else 0, kv_norm.data_ptr() if kv is not None else 0, cos.data_ptr(),
+        q.data_ptr(), q.stride(0), folded.data_ptr() if folded is not None else 0,
+        folded.stride(0) if folded is not None else 0, kv.data_ptr() if kv is not None else 0,
+        kv.stride(0) if kv is not None else 0, 1 if write_back else 0, 1 if folded is None else 0, kv_norm.data_ptr() if kv is not None else 0, cos.data_ptr(),
         sin.data_ptr(), tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), tables.seq_slot.data_ptr(),
         kv_view.keys.data_ptr() if kv is not None else 0, cache_geometry(kv_view if kv is not None else None, 1,
                                                                          rank + rot_dim),
@@ -94,3 +102,41 @@ def attention(folded: torch.Tensor, out: torch.Tensor, *, heads: int, rank: int,
                          rank, rot_dim, int(window or 0), float(scale))
     _check(library().kidi_latent_attention(ctypes.byref(args), dtype_code(folded.dtype), ops._stream()),
            "latent_attention")
+
+
+class PackArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("ldq", c_longlong), ("latent", c_void_p), ("ldl", c_longlong), ("unfolded", c_void_p),
+                ("ldu", c_longlong), ("packed", c_void_p), ("ldp", c_longlong), ("cos_table", c_void_p),
+                ("sin_table", c_void_p), ("row_seq", c_void_p), ("row_pos", c_void_p), ("rows", c_int), ("heads", c_int),
+                ("dim", c_int), ("rot_dim", c_int), ("rotary_dims", c_int), ("rank", c_int), ("vdim", c_int)]
+
+
+def pack(q: torch.Tensor, latent: torch.Tensor, unfolded: torch.Tensor, *, heads: int, dim: int, rot_dim: int,
+         rank: int, vdim: int, rotary_dims: int, cos: torch.Tensor, sin: torch.Tensor, tables) -> torch.Tensor:
+    """The matrix [rows, 3 * heads * (dim + rot_dim)] of queries (rotated here), keys and zero-padded values that
+    the prompt attention kernels take, from q [rows, heads * (dim + rot_dim)], the rows' cache entries `latent`
+    [rows, rank + rot_dim] and `unfolded` [rows, heads * dim + heads * vdim] (plain keys, then values)."""
+    ops._need_cuda(q, latent, unfolded, cos, sin)
+    rows, width = q.shape[0], dim + rot_dim
+    if q.shape != (rows, heads * width) or latent.shape != (rows, rank + rot_dim) \
+            or unfolded.shape != (rows, heads * (dim + vdim)) or vdim > width \
+            or any(t.stride(1) != 1 or t.dtype != q.dtype for t in (q, latent, unfolded)):
+        raise invalid_argument("latent pack: the shapes do not fit")
+    packed = torch.empty((rows, 3 * heads * width), dtype=q.dtype, device=q.device)
+    args = PackArgs(q.data_ptr(), q.stride(0), latent.data_ptr(), latent.stride(0), unfolded.data_ptr(),
+                    unfolded.stride(0), packed.data_ptr(), packed.stride(0), cos.data_ptr(), sin.data_ptr(),
+                    tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), rows, heads, dim, rot_dim, rotary_dims, rank,
+                    vdim)
+    _check(library().kidi_latent_pack(ctypes.byref(args), dtype_code(q.dtype), ops._stream()), "latent_pack")
+    return packed
+
+
+def gather(kv_view, rows: int, width: int, tables) -> torch.Tensor:
+    """The cache entries of the step's rows as a matrix [rows, width]."""
+    out = torch.empty((rows, width), dtype=kv_view.keys.dtype, device=kv_view.keys.device)
+    geometry = cache_geometry(kv_view, 1, width)
+    _check(library().kidi_latent_gather(kv_view.keys.data_ptr(), ctypes.byref(geometry), out.data_ptr(), out.stride(0),
+                                        tables.row_seq.data_ptr(), tables.row_pos.data_ptr(),
+                                        tables.seq_slot.data_ptr(), rows, width, dtype_code(out.dtype), ops._stream()),
+           "latent_gather")
+    return out

@@ -9,14 +9,14 @@ import torch
 from ..csrc.build import load_library
 from ..errors import invalid_argument
 from . import ops
-from .ops import _check, c_float, c_int, c_longlong, c_void_p, dtype_code
+from .ops import _check, c_int, c_longlong, c_void_p, dtype_code
 
 
 class RecurrenceArgs(ctypes.Structure):
-    _fields_ = [("qfv", c_void_p), ("ld", c_longlong), ("f_bias", c_void_p), ("lower", c_void_p), ("norm", c_void_p),
+    _fields_ = [("qfv", c_void_p), ("ld", c_longlong), ("f_bias", c_void_p), ("lower", c_void_p),
                 ("state", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p),
                 ("seq_slot", c_void_p), ("seq_row0", c_void_p), ("seq_len", c_void_p), ("seqs", c_int),
-                ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("groups", c_int), ("eps", c_float)]
+                ("heads", c_int), ("dim", c_int), ("vdim", c_int)]
 
 
 _library = None
@@ -33,23 +33,24 @@ def library():
 
 
 def gated_recurrence(qfv: torch.Tensor, out: torch.Tensor, state: torch.Tensor, *, f_bias: torch.Tensor,
-                     lower: torch.Tensor, norm: torch.Tensor, heads: int, dim: int, vdim: int, eps: float, tables,
-                     seqs: int) -> None:
+                     lower: torch.Tensor, heads: int, dim: int, vdim: int, tables, seqs: int) -> None:
     """Runs every sequence's rows of the step through the recurrence, from and into `state`
     [slots + 1, heads, dim, vdim] (float32). qfv [rows, 2*heads*dim + heads*vdim] holds the raw projections
-    [q | f | v]; out [rows, heads*vdim] gets each head's normalised read-out."""
-    ops._need_cuda(qfv, out, state, f_bias, lower, norm)
+    [q | f | v]; out [rows, heads*vdim] gets each head's read-out S^T q, not yet normalised."""
+    ops._need_cuda(qfv, out, state, f_bias, lower)
     rows = qfv.shape[0]
     if qfv.shape != (rows, 2 * heads * dim + heads * vdim) or out.shape != (rows, heads * vdim) or out.dtype != qfv.dtype \
             or qfv.stride(1) != 1 or out.stride(1) != 1:
         raise invalid_argument("gated recurrence: projections or output have the wrong shape")
     if state.dtype != torch.float32 or state.shape[1:] != (heads, dim, vdim) or not state.is_contiguous():
         raise invalid_argument("gated recurrence: the state is float32 [slots, heads, dim, vdim]")
-    for vector, size in ((f_bias, heads * dim), (lower, heads * dim), (norm, vdim)):
+    if dim > 256:
+        raise invalid_argument("gated recurrence: the kernel takes up to 256 state rows a head")
+    for vector, size in ((f_bias, heads * dim), (lower, heads * dim)):
         if vector.dtype != torch.float32 or vector.shape != (size,) or not vector.is_contiguous():
-            raise invalid_argument("gated recurrence: bias, lower bound and norm weight are float32 vectors")
-    args = RecurrenceArgs(qfv.data_ptr(), qfv.stride(0), f_bias.data_ptr(), lower.data_ptr(), norm.data_ptr(),
+            raise invalid_argument("gated recurrence: bias and lower bound are float32 vectors")
+    args = RecurrenceArgs(qfv.data_ptr(), qfv.stride(0), f_bias.data_ptr(), lower.data_ptr(),
                           state.data_ptr(), out.data_ptr(), out.stride(0), tables.row_seq.data_ptr(),
                           tables.seq_slot.data_ptr(), tables.seq_row0.data_ptr(), tables.seq_len.data_ptr(), seqs,
-                          heads, dim, vdim, 0, float(eps))
+                          heads, dim, vdim)
     _check(library().kidi_gated_recurrence(ctypes.byref(args), dtype_code(qfv.dtype), ops._stream()), "gated_recurrence")

@@ -21,7 +21,8 @@ from typing import List, Optional
 import torch
 
 from ..cache.sequence_cache import StateRequest
-from ..errors import invalid_argument
+from ..errors import invalid_argument, unsupported
+from ..kernels import ops
 from ..kernels import recurrence as recurrence_kernels
 from .base import Part, plain_rows
 from .linear import Linear
@@ -42,6 +43,8 @@ class GatedRecurrence(Part):
         self.eps = float(spec.param("eps"))
         if min(self.hidden, self.heads, self.dim, self.vdim) <= 0:
             raise invalid_argument("invalid recurrence dimensions")
+        if self.dim > 256:
+            raise unsupported(f"a recurrent head of {self.dim} state rows exceeds 256, the most the kernel takes")
         self.names = {key: spec.param(key + "_name", default) for key, default in NAMES.items()}
         self.qfv: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -75,7 +78,7 @@ class GatedRecurrence(Part):
             raise invalid_argument("a recurrent layer keeps a state of its own")
         qfv = self.qfv.forward(plain_rows(x))
         read = torch.empty((qfv.shape[0], self.heads * self.vdim), dtype=qfv.dtype, device=qfv.device)
-        recurrence_kernels.gated_recurrence(qfv, read, views[0], f_bias=self.f_bias, lower=self.lower, norm=self.norm,
-                                            heads=self.heads, dim=self.dim, vdim=self.vdim, eps=self.eps,
-                                            tables=ctx.tables, seqs=ctx.plan.n_seqs)
-        return self.out.forward(read)
+        recurrence_kernels.gated_recurrence(qfv, read, views[0], f_bias=self.f_bias, lower=self.lower,
+                                            heads=self.heads, dim=self.dim, vdim=self.vdim, tables=ctx.tables,
+                                            seqs=ctx.plan.n_seqs)
+        return self.out.forward(ops.rms_rows(read, self.vdim, self.norm, self.eps, out=read))

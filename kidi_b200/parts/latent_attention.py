@@ -8,8 +8,13 @@ W_uk[i] c, its value W_uv[i] c; a score is (q_plain . k_plain + q_rot . k_rot) *
 heads back. The rotation pairs entries 2i and 2i+1 of the rotated part (the named position encoding gives the
 angles).
 
-The key map is folded into the query (q_lat = W_uk[i]^T q_plain, per head) and the value map is applied to the
-weighted sum of latents, so attention reads the cached rows only: it never materialises per-head keys or values.
+Two forms compute the same thing. Folded: the key map is folded into the query (q_lat = W_uk[i]^T q_plain, per
+head) and the value map is applied to the weighted sum of latents, so attention reads the cached rows only and
+never materialises per-head keys or values: decoding, prompts that continue cached sequences, and everything in
+32-bit. Unfolded: for bfloat16 prompts that start at position 0 every head's keys and values are computed from
+the latents of the step's own rows, packed with the queries into the matrix that this package's tensor-core prompt
+attention kernels take (values zero-padded to the key width, W_o's columns padded to match), and attention costs
+dim + rot_dim + vdim multiply-adds per score instead of 2 kv_rank + rot_dim.
 
 A layer with `kv_from` set has no W_dkv and reads the cache of the layer that is named as its cache source in
 the schedule; its own W_uk, W_uv, queries and mask apply.
@@ -26,6 +31,7 @@ import torch
 
 from ..cache.sequence_cache import KVRequest
 from ..errors import invalid_argument, unsupported
+from ..kernels import attention as attention_kernels
 from ..kernels import latent as latent_kernels
 from ..kernels import ops
 from .base import Part, plain_rows
@@ -94,6 +100,28 @@ class LatentAttention(Part):
         if self.owns_latent:
             self.dkv = Linear(tensors[n["dkv"]])
             self.dkv_norm = tensors[n["dkv_norm"]].float().contiguous()
+        self._uk, self._uv, self._o = tensors[n["uk"]], tensors[n["uv"]], tensors[n["o"]]
+        self._unfold = None      # (Linear of [W_uk; W_uv], Linear of W_o with padded columns), made at first use
+
+    def _unfolded_maps(self):
+        if self._unfold is None:
+            width = self.dim + self.rot_dim
+            out = self._o
+            if self.vdim < width:     # the attention kernel's result has `width` values a head, the last ones zero
+                out = torch.zeros((self.hidden, self.heads, width), dtype=out.dtype, device=out.device)
+                out[:, :, :self.vdim] = self._o.view(self.hidden, self.heads, self.vdim)
+                out = out.view(self.hidden, self.heads * width)
+            self._unfold = (Linear(torch.cat([self._uk, self._uv], dim=0).contiguous()), Linear(out))
+        return self._unfold
+
+    def _unfolds(self, x, ctx, view) -> bool:
+        """Whether this step takes the unfolded form: bfloat16 prompts that all start at position 0, with head
+        widths the tensor-core prompt kernels take."""
+        plan, width = ctx.plan, self.dim + self.rot_dim
+        return (x.dtype == torch.bfloat16 and not plan.is_decode and int(plan.seq_start.max()) == 0
+                and self.vdim <= width and self.window is None
+                and attention_kernels.fast_fits(x.dtype, self.heads, self.heads, width, False)
+                and (view is None or view.page_size == 64))
 
     def cache_requests(self) -> list:
         # One row [c | rotated key part] per token and no values of their own: the values are maps of c.
@@ -111,6 +139,8 @@ class LatentAttention(Part):
         heads, rank, rot_dim = self.heads, self.rank, self.rot_dim
         q = self.uq.forward(ops.rms_rows(self.dq.forward(x), self.q_rank, self.dq_norm, self.eps))
         kv = self.dkv.forward(x) if self.owns_latent else None
+        if self._unfolds(x, ctx, view):
+            return self._forward_unfolded(q, kv, ctx, view)
         folded = torch.empty((rows, heads * (rank + rot_dim)), dtype=q.dtype, device=q.device)
         position = self.position
         latent_kernels.prepare(q, folded, kv, self.dkv_norm, heads=heads, dim=self.dim, rot_dim=rot_dim, rank=rank,
@@ -127,3 +157,22 @@ class LatentAttention(Part):
         attended = torch.empty((rows, heads * self.vdim), dtype=q.dtype, device=q.device)
         ops.gemm_heads(summed.view(rows, heads, rank), self.uv, attended.view(rows, heads, self.vdim))
         return self.out.forward(attended)
+
+    def _forward_unfolded(self, q, kv, ctx, view) -> torch.Tensor:
+        rows, heads, width = q.shape[0], self.heads, self.dim + self.rot_dim
+        position = self.position
+        rotation = dict(rotary_dims=position.rotary_dim, cos=position.cos, sin=position.sin)
+        if self.owns_latent:
+            latent_kernels.prepare(q, None, kv, self.dkv_norm, heads=heads, dim=self.dim, rot_dim=self.rot_dim,
+                                   rank=self.rank, eps=self.eps, tables=ctx.tables, kv_view=view, write_back=True,
+                                   **rotation)
+        else:
+            kv = latent_kernels.gather(view, rows, self.rank + self.rot_dim, ctx.tables)
+        unfold, out = self._unfolded_maps()
+        unfolded = unfold.forward(kv[:, :self.rank])
+        packed = latent_kernels.pack(q, kv, unfolded, heads=heads, dim=self.dim, rot_dim=self.rot_dim, rank=self.rank,
+                                     vdim=self.vdim, tables=ctx.tables, **rotation)
+        attended = torch.empty((rows, heads * width), dtype=q.dtype, device=q.device)
+        attention_kernels.run(ctx, packed, attended, heads=heads, kv_heads=heads, head_dim=width, scale=self.scale,
+                              window=None, kv_view=None, keys_in_step=True)
+        return out.forward(attended)

@@ -255,3 +255,38 @@ def test_the_command_line_generates(tmp_path, capsys):
     for record in records:
         request = requests[int(record["id"])]
         assert teacher_forced(config, tensors, request, record["token_ids"], LARGEST["float32"]) == 0
+
+
+def test_which_kernels_run(record_property):
+    """bfloat16 prompts from position 0 take the unfolded form (keys and values per head through the tensor-core
+    prompt kernels: tcgen05 where a head's plain and rotated widths add up to 64 or 128); decoding, later portions
+    and the 32-bit engine take the folded form over the cached latents. Both forms agree within rounding."""
+    from kidi_b200 import StepBatch
+    from kidi_b200.kernels import ops
+    engine, config, tensors = make("wide", "bfloat16", seed=3)
+    tokens = prompt(config, 200, 5)
+    slot = engine.acquire()
+    with ops.record_launches() as names:
+        whole = run(engine, slot, tokens)
+    engine.release(slot)
+    assert names.count("latent_pack") == 3 and names.count("latent_gather") == 1 and "latent_attention" not in names
+    assert names.count("attention_prefill_tcgen05") == 2 and names.count("attention_prefill[mma.sync]") == 1
+    assert names.count("gated_recurrence") == 2 and names.count("add_layernorm") == 5 + 3 + 1
+    slot = engine.acquire()
+    run(engine, slot, tokens[:1], want=[])
+    with ops.record_launches() as names:
+        rest = run(engine, slot, tokens[1:])          # continues a cached sequence: the folded form
+    with ops.record_launches() as decode_names:
+        engine.step(StepBatch([slot], [[7]], None))
+    engine.release(slot)
+    assert names.count("latent_attention") == 3 and "latent_pack" not in names
+    assert decode_names.count("latent_attention") == 3 and decode_names.count("gated_recurrence") == 2
+    difference = float((rest - whole[1:]).pow(2).mean().sqrt() / whole.pow(2).mean().sqrt())
+    record_property("folded against unfolded, mean relative difference", difference)
+    assert difference < 0.05
+    engine32, _, _ = make("wide", "float32", seed=3)
+    slot = engine32.acquire()
+    with ops.record_launches() as names:
+        run(engine32, slot, tokens)
+    assert names.count("latent_attention") == 3 and "latent_pack" not in names and "library_mm" not in names
+    assert not any("tcgen05" in name or "skinny" in name for name in names)
