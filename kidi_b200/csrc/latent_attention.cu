@@ -294,3 +294,271 @@ KIDI_API int kidi_latent_gather(const void* cache, const CacheGeometry* geometry
                            ldo, row_seq, row_pos, seq_slot, width);
     return KIDI_REFUSED_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// The folded form on the tensor cores (bfloat16; rank and rot_dim multiples of 16, rank <= 512, pages of 64
+// tokens, no window). A block of four warps takes one row of the step, a tile of up to 16 of its heads and a share
+// of its sequence's pages. A page [64 tokens, W = rank + rot_dim] is copied to shared memory once (cp.async) and
+// serves as the keys of S = Q K^T (all W columns) and, its first `rank` columns, as the values of O += P C: the
+// cached rows are read once for all heads of the tile. Warp w computes the scores of the page's tokens 16w..16w+15
+// for the 16 heads (`mma.sync` m16n8k16, fragments by `ldmatrix`), the warps exchange row maxima and sums through
+// shared memory (online softmax in 32-bit), P goes to shared memory in bfloat16, and warp w accumulates the output
+// columns of its n-tiles (tile i belongs to warp i mod 4) with the page as a transposed B operand
+// (`ldmatrix.trans`). Every block leaves (O, max, sum) of its share in a workspace; `latent_combine` merges the
+// shares of a (row, head) in their order.
+struct LatentDecodeArgs {
+    const void* folded;     // [rows, ldf]: per head [q_lat (rank) | q_rot (rot_dim)], bfloat16
+    long long ldf;
+    const void* cache;      // [pages, 64, W] bfloat16
+    const int* table;       // [slots, pages_per_seq]
+    int pages_per_seq;
+    const int* row_seq;
+    const int* row_pos;
+    const int* seq_slot;
+    float* part_o;          // [rows, splits, heads, rank]
+    float* part_stat;       // [rows, splits, heads, 2]: max, sum
+    void* out;              // [rows, ldo] bfloat16 (combine)
+    long long ldo;
+    int rows, heads, rank, rot_dim, splits;
+    float scale;
+};
+
+namespace {
+__device__ __forceinline__ unsigned shared_address(const void* pointer) {
+    return (unsigned)__cvta_generic_to_shared(pointer);
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], unsigned address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void copy_async_16(unsigned destination, const void* source) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(destination), "l"(source));
+}
+
+constexpr int PAGE = 64;
+
+template <int TILES>   // output n-tiles (8 columns) a warp owns at most: rank <= 32 * TILES
+__global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int row = blockIdx.x, head0 = blockIdx.y * 16, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int W = a.rank + a.rot_dim, stride = W + 8;      // padded rows: ldmatrix without bank conflicts
+    bf16* Qs = reinterpret_cast<bf16*>(raw);                // [16][stride]
+    bf16* Ks = Qs + 16 * stride;                            // [64][stride]
+    bf16* Ps = Ks + PAGE * stride;                          // [16][PAGE + 8]
+    float* wmax = reinterpret_cast<float*>(Ps + 16 * (PAGE + 8));   // [4][16]
+    float* wsum = wmax + 64;                                // [4][16]
+    const int heads_here = min(16, a.heads - head0);
+    float* part_o = a.part_o + (((long long)row * a.splits + split) * a.heads + head0) * a.rank;
+    float* part_stat = a.part_stat + (((long long)row * a.splits + split) * a.heads + head0) * 2;
+    const int seq = a.row_seq[row];
+    int first_page = 0, last_page = 0, position = -1, slot = 0;
+    if (seq >= 0) {
+        position = a.row_pos[row];
+        slot = a.seq_slot[seq];
+        const int pages = (position >> 6) + 1;
+        const int per = (pages + a.splits - 1) / a.splits;
+        first_page = split * per;
+        last_page = min(pages, first_page + per);
+    }
+    if (first_page >= last_page) {                          // nothing to do: an empty share
+        if (threadIdx.x < heads_here) {
+            part_stat[threadIdx.x * 2] = -INFINITY;
+            part_stat[threadIdx.x * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    // the tile's queries, zero rows beyond the heads
+    const bf16* q = (const bf16*)a.folded + row * a.ldf + (long long)head0 * W;
+    const int chunks = W / 8;                               // 16-byte pieces of a row
+    for (int index = threadIdx.x; index < 16 * chunks; index += 128) {
+        const int h = index / chunks, c = (index - h * chunks) * 8;
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (h < heads_here) value = *reinterpret_cast<const uint4*>(q + (long long)h * W + c);
+        *reinterpret_cast<uint4*>(Qs + h * stride + c) = value;
+    }
+    float o[TILES][4];
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float best[2] = {-INFINITY, -INFINITY}, denom[2] = {0.f, 0.f};   // of rows g and g + 8
+    const int n_tiles = a.rank / 8;
+    for (int page_index = first_page; page_index < last_page; ++page_index) {
+        const int page = a.table[(long long)slot * a.pages_per_seq + page_index];
+        const bf16* source = (const bf16*)a.cache + (long long)page * PAGE * W;
+        __syncthreads();                                    // the last page's products have read Ks and Ps
+        for (int index = threadIdx.x; index < PAGE * chunks; index += 128) {
+            const int r = index / chunks, c = (index - r * chunks) * 8;
+            copy_async_16(shared_address(Ks + r * stride + c), source + (long long)r * W + c);
+        }
+        asm volatile("cp.async.commit_group;");
+        asm volatile("cp.async.wait_group 0;");
+        __syncthreads();
+        // scores of tokens 16 warp .. 16 warp + 15 against the 16 heads
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        for (int k0 = 0; k0 < W; k0 += 16) {
+            unsigned qa[4], kb[4];
+            ldmatrix_x4(qa, shared_address(Qs + (lane & 15) * stride + k0 + (lane >> 4) * 8));
+            const int mi = lane >> 3;
+            ldmatrix_x4(kb, shared_address(Ks + (16 * warp + (mi >> 1) * 8 + (lane & 7)) * stride + k0 + (mi & 1) * 8));
+            mma_bf16(s[0], qa, kb[0], kb[1]);
+            mma_bf16(s[1], qa, kb[2], kb[3]);
+        }
+        const int token0 = page_index * PAGE + 16 * warp + 2 * t;
+        float top[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int token = token0 + 8 * j + (e & 1);
+                s[j][e] = token <= position ? s[j][e] * a.scale : -INFINITY;
+                top[e >> 1] = fmaxf(top[e >> 1], s[j][e]);
+            }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
+            top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 2));
+        }
+        if (t == 0) { wmax[warp * 16 + g] = top[0]; wmax[warp * 16 + g + 8] = top[1]; }
+        __syncthreads();
+        float next[2], keep[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int h = g + 8 * r;
+            const float tile = fmaxf(fmaxf(wmax[h], wmax[16 + h]), fmaxf(wmax[32 + h], wmax[48 + h]));
+            next[r] = fmaxf(best[r], tile);                 // finite: the page holds a token at or before the position
+            keep[r] = expf(best[r] - next[r]);              // 0 on the first page
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = expf(s[j][e] - next[e >> 1]);
+                sum[e >> 1] += p[e];
+            }
+            const int column = 16 * warp + 8 * j + 2 * t;
+            *reinterpret_cast<__nv_bfloat162*>(Ps + g * (PAGE + 8) + column) = __floats2bfloat162_rn(p[0], p[1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * (PAGE + 8) + column) = __floats2bfloat162_rn(p[2], p[3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        }
+        if (t == 0) { wsum[warp * 16 + g] = sum[0]; wsum[warp * 16 + g + 8] = sum[1]; }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int h = g + 8 * r;
+            denom[r] = denom[r] * keep[r] + ((wsum[h] + wsum[16 + h]) + (wsum[32 + h] + wsum[48 + h]));
+            best[r] = next[r];
+        }
+        // O = O * keep + P C over this warp's n-tiles
+        unsigned pa[4][4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            ldmatrix_x4(pa[k], shared_address(Ps + (lane & 15) * (PAGE + 8) + 16 * k + (lane >> 4) * 8));
+#pragma unroll
+        for (int i = 0; i < TILES; i += 2) {                // two n-tiles a ldmatrix: tiles n and n + 4 of this warp
+            const int n_first = warp + 4 * i, n_second = warp + 4 * (i + 1);
+            if (n_first >= n_tiles) break;
+            o[i][0] *= keep[0]; o[i][1] *= keep[0]; o[i][2] *= keep[1]; o[i][3] *= keep[1];
+            o[i + 1][0] *= keep[0]; o[i + 1][1] *= keep[0]; o[i + 1][2] *= keep[1]; o[i + 1][3] *= keep[1];
+            const bool both = n_second < n_tiles;
+            const int mi = lane >> 3;
+            const int column = ((mi >> 1) && both ? n_second : n_first) * 8;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                unsigned cb[4];
+                ldmatrix_x4_trans(cb, shared_address(Ks + (16 * k + (mi & 1) * 8 + (lane & 7)) * stride + column));
+                mma_bf16(o[i], pa[k], cb[0], cb[1]);
+                if (both) mma_bf16(o[i + 1], pa[k], cb[2], cb[3]);
+            }
+        }
+    }
+    // this share's result
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) {
+        const int n = warp + 4 * i;
+        if (n >= n_tiles) break;
+        const int column = n * 8 + 2 * t;
+        if (g < heads_here) *reinterpret_cast<float2*>(part_o + (long long)g * a.rank + column) = make_float2(o[i][0], o[i][1]);
+        if (g + 8 < heads_here)
+            *reinterpret_cast<float2*>(part_o + (long long)(g + 8) * a.rank + column) = make_float2(o[i][2], o[i][3]);
+    }
+    if (warp == 0 && t == 0) {
+        if (g < heads_here) { part_stat[g * 2] = best[0]; part_stat[g * 2 + 1] = denom[0]; }
+        if (g + 8 < heads_here) { part_stat[(g + 8) * 2] = best[1]; part_stat[(g + 8) * 2 + 1] = denom[1]; }
+    }
+}
+
+// out[row, head, :] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(max_s - max), over the shares in their order.
+__global__ void __launch_bounds__(128) latent_combine_kernel(LatentDecodeArgs a) {
+    const int row = blockIdx.x, head = blockIdx.y;
+    bf16* out = (bf16*)a.out + row * a.ldo + (long long)head * a.rank;
+    const float* stat = a.part_stat + ((long long)row * a.splits * a.heads + head) * 2;
+    const float* part = a.part_o + ((long long)row * a.splits * a.heads + head) * a.rank;
+    const long long step = (long long)a.heads;
+    float top = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) top = fmaxf(top, stat[s * step * 2]);
+    if (a.row_seq[row] < 0 || top == -INFINITY) {
+        for (int c = threadIdx.x; c < a.rank; c += 128) out[c] = from_float<bf16>(0.f);
+        return;
+    }
+    float total = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+        const float m = stat[s * step * 2];
+        if (m != -INFINITY) total += stat[s * step * 2 + 1] * expf(m - top);
+    }
+    for (int c = threadIdx.x; c < a.rank; c += 128) {
+        float value = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float m = stat[s * step * 2];
+            if (m != -INFINITY) value += part[s * step * a.rank + c] * expf(m - top);
+        }
+        out[c] = from_float<bf16>(value / total);
+    }
+}
+
+template <int TILES>
+int launch_decode(const LatentDecodeArgs& a, cudaStream_t stream) {
+    const int W = a.rank + a.rot_dim;
+    const size_t shared = (size_t)(16 + PAGE) * (W + 8) * 2 + 16 * (PAGE + 8) * 2 + 128 * sizeof(float);
+    auto kernel = latent_decode_kernel<TILES>;
+    if (shared > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) return (int)status;
+    }
+    dim3 grid(a.rows, (a.heads + 15) / 16, a.splits);
+    const int status = kidi_launch(kernel, grid, 128, shared, stream, a);
+    if (status) return status;
+    return kidi_launch(latent_combine_kernel, dim3(a.rows, a.heads), 128, 0, stream, a);
+}
+}  // namespace
+
+// How many floats of workspace a launch needs (part_o, then part_stat).
+KIDI_API long long kidi_latent_decode_workspace(int rows, int heads, int rank, int splits) {
+    return (long long)rows * splits * heads * (rank + 2);
+}
+
+KIDI_API int kidi_latent_decode(const LatentDecodeArgs* args, cudaStream_t stream) {
+    const LatentDecodeArgs& a = *args;
+    if (a.rows <= 0) return 0;
+    if (a.heads <= 0 || (a.heads + 15) / 16 > 65535 || a.splits <= 0 || a.splits > 65535 || a.rank <= 0 || (a.rank & 15) ||
+        (a.rot_dim & 15) || a.rank > 512 || a.rot_dim < 0 || a.rank + a.rot_dim > 1024 || (a.ldf & 7) ||
+        ((uintptr_t)a.folded & 15) || ((uintptr_t)a.cache & 15))
+        return KIDI_REFUSED_SIZE;
+    if (a.rank <= 128) return launch_decode<4>(a, stream);
+    if (a.rank <= 256) return launch_decode<8>(a, stream);
+    return launch_decode<16>(a, stream);
+}

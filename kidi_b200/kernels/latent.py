@@ -44,7 +44,11 @@ def library():
         lib.kidi_latent_pack.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_latent_gather.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                                            c_int, c_int, c_void_p]
-        for name in ("kidi_latent_prepare", "kidi_latent_attention", "kidi_latent_pack", "kidi_latent_gather"):
+        lib.kidi_latent_decode.argtypes = [c_void_p, c_void_p]
+        lib.kidi_latent_decode_workspace.argtypes = [c_int, c_int, c_int, c_int]
+        lib.kidi_latent_decode_workspace.restype = c_longlong
+        for name in ("kidi_latent_prepare", "kidi_latent_attention", "kidi_latent_pack", "kidi_latent_gather",
+                     "kidi_latent_decode"):
             getattr(lib, name).restype = c_int
         _library = lib
     return _library
@@ -140,3 +144,48 @@ def gather(kv_view, rows: int, width: int, tables) -> torch.Tensor:
                                         tables.seq_slot.data_ptr(), rows, width, dtype_code(out.dtype), ops._stream()),
            "latent_gather")
     return out
+
+
+class DecodeArgs(ctypes.Structure):
+    _fields_ = [("folded", c_void_p), ("ldf", c_longlong), ("cache", c_void_p), ("table", c_void_p),
+                ("pages_per_seq", c_int), ("row_seq", c_void_p), ("row_pos", c_void_p), ("seq_slot", c_void_p),
+                ("part_o", c_void_p), ("part_stat", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("rows", c_int),
+                ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("scale", c_float)]
+
+
+def tensor_core_fits(dtype: torch.dtype, rank: int, rot_dim: int, window, kv_view) -> bool:
+    """Whether the folded form can run on the tensor cores: bfloat16, widths in multiples of 16, a latent of at
+    most 512 values, a cache of 64-token pages that keeps every page."""
+    return (dtype == torch.bfloat16 and rank % 16 == 0 and rot_dim % 16 == 0 and 0 < rank <= 512 and window is None
+            and (kv_view is None or (kv_view.page_size == 64 and kv_view.ring_pages == 0
+                                     and kv_view.keys.is_contiguous() and kv_view.table.is_contiguous())))
+
+
+def decode_splits(rows: int, heads: int, longest: int, device: torch.device) -> int:
+    """How many blocks share a sequence's pages: as many as fill the GPU about twice, at most one a page."""
+    from .attention import sm_count
+    pages = max(1, -(-longest // 64))
+    tiles = -(-heads // 16)
+    return max(1, min(pages, (2 * sm_count(device)) // max(1, rows * tiles)))
+
+
+def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads: int, rank: int, rot_dim: int,
+                          scale: float, kv_view, splits: Optional[int] = None) -> None:
+    """The folded form on the tensor cores (see `attention`), every row of the step against its sequence's pages;
+    the shares of a row's pages meet in a workspace and a second kernel merges them."""
+    ops._need_cuda(folded, out)
+    rows = folded.shape[0]
+    if folded.shape != (rows, heads * (rank + rot_dim)) or out.shape != (rows, heads * rank) or folded.stride(1) != 1 \
+            or out.stride(1) != 1 or folded.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 \
+            or kv_view.keys.shape[-1] != rank + rot_dim:
+        raise invalid_argument("latent attention: folded queries, output or cache have the wrong shape")
+    splits = splits or decode_splits(rows, heads, ctx.plan.max_total, folded.device)
+    count = int(library().kidi_latent_decode_workspace(rows, heads, rank, splits))
+    workspace = ctx.workspace("latent_partial", count)
+    tables = ctx.tables
+    args = DecodeArgs(folded.data_ptr(), folded.stride(0), kv_view.keys.data_ptr(), kv_view.table.data_ptr(),
+                      kv_view.table.shape[1], tables.row_seq.data_ptr(), tables.row_pos.data_ptr(),
+                      tables.seq_slot.data_ptr(), workspace.data_ptr(),
+                      workspace.data_ptr() + rows * splits * heads * rank * 4, out.data_ptr(), out.stride(0), rows,
+                      heads, rank, rot_dim, splits, float(scale))
+    _check(library().kidi_latent_decode(ctypes.byref(args), ops._stream()), f"latent_attention[mma.sync, {splits} shares]", 2)

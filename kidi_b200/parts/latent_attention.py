@@ -11,7 +11,8 @@ angles).
 Two forms compute the same thing. Folded: the key map is folded into the query (q_lat = W_uk[i]^T q_plain, per
 head) and the value map is applied to the weighted sum of latents, so attention reads the cached rows only and
 never materialises per-head keys or values: decoding, prompts that continue cached sequences, and everything in
-32-bit. Unfolded: for bfloat16 prompts that start at position 0 every head's keys and values are computed from
+32-bit (bfloat16 with widths in multiples of 16 on the tensor cores, a page of cached rows read once for 16 heads;
+else on the general kernel). Unfolded: for bfloat16 prompts that start at position 0 every head's keys and values are computed from
 the latents of the step's own rows, packed with the queries into the matrix that this package's tensor-core prompt
 attention kernels take (values zero-padded to the key width, W_o's columns padded to match), and attention costs
 dim + rot_dim + vdim multiply-adds per score instead of 2 kv_rank + rot_dim.
@@ -128,6 +129,13 @@ class LatentAttention(Part):
         return [KVRequest(1, self.rank + self.rot_dim, int(self.window) if self.window is not None else None,
                           value_dim=0)]
 
+    def launch_signature(self, rows: int, longest: int) -> tuple:
+        """What a captured decode step freezes: into how many shares the tensor-core kernel cuts a sequence's
+        pages (the general kernel, which the 32-bit engine runs, has no such choice)."""
+        if not latent_kernels.tensor_core_fits(self.env.dtype, self.rank, self.rot_dim, self.window, None):
+            return ()
+        return (latent_kernels.decode_splits(rows, self.heads, longest, self.env.device),)
+
     def forward(self, x, ctx, views, owns_cache: bool, sink=None) -> Optional[torch.Tensor]:
         x = plain_rows(x)
         view = views[0]
@@ -152,8 +160,12 @@ class LatentAttention(Part):
         else:
             folded.view(rows, heads, rank + rot_dim)[:, :, :rank].zero_()
         summed = torch.empty((rows, heads * rank), dtype=q.dtype, device=q.device)
-        latent_kernels.attention(folded, summed, heads=heads, rank=rank, rot_dim=rot_dim, scale=self.scale,
-                                 window=self.window, tables=ctx.tables, kv_view=view)
+        if latent_kernels.tensor_core_fits(q.dtype, rank, rot_dim, self.window, view):
+            latent_kernels.attention_tensor_core(ctx, folded, summed, heads=heads, rank=rank, rot_dim=rot_dim,
+                                                 scale=self.scale, kv_view=view)
+        else:
+            latent_kernels.attention(folded, summed, heads=heads, rank=rank, rot_dim=rot_dim, scale=self.scale,
+                                     window=self.window, tables=ctx.tables, kv_view=view)
         attended = torch.empty((rows, heads * self.vdim), dtype=q.dtype, device=q.device)
         ops.gemm_heads(summed.view(rows, heads, rank), self.uv, attended.view(rows, heads, self.vdim))
         return self.out.forward(attended)

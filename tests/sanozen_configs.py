@@ -44,13 +44,13 @@ SMALL_B = model(131, 72, 1.0, 3e-6, 5, [
     latent(5, 8, 24, 8, 28, 24, 0.22, 1000000.0, 24, ff=72, kv_from=2),
 ])
 
-# wider: the plain and rotated widths of a head add up to 64 and to 128, the widths of the tensor-core prompt
-# kernels, with narrower values; sharp scores so that single far keys carry a row's result
+# wider: the plain and rotated widths of a head add up to 64 and to 128, the widths of the tcgen05 prompt kernel,
+# and to 80 (the mma.sync one), with values narrower than, and as wide as, the keys; sharper scores
 WIDE = model(211, 256, 8.0, 1e-5, 16, [
     latent(4, 32, 32, 48, 64, 96, 0.6, 10000.0, 32, ff=320),
     recurrent(2, 64, 64),
     latent(2, 96, 32, 128, 48, 96, 0.5, 10000.0, 32, ff=256, kv_from=0),
-    latent(3, 48, 16, 64, 40, 160, 0.7, 300000.0, 16),
+    latent(3, 64, 16, 64, 40, 160, 0.7, 300000.0, 16),
     recurrent(4, 32, 48, ff=192),
 ])
 
