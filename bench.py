@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--model 8b|14b|32b] [--impl ours|reference]
+    python bench.py --design sanozen [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
 
 A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
 layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
@@ -283,8 +284,183 @@ def time_end_to_end(engine, prompts, steps: int):
     return batch * stats.decode_steps / (stats.decode_ns / 1e9), stats, found
 
 
+# ---------------------------------------------------------------------------------------------- --design sanozen
+def sanozen_shape(width: int, layers: int = 4) -> dict:
+    """A Sanozen stack at the layer sizes of a model of `width`: heads of 128 (64 plain + 64 rotated query/key
+    dimensions, values of 128), a latent of width / 8, query latents of 3 width / 8, recurrent heads of 128 x 128,
+    dense feed-forwards of 4 width; latent attention and recurrence in turn, every other attention layer reading
+    the cached rows of the one before it."""
+    heads = width // 128
+    attention = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 8,
+                 "kv_rank": width // 8, "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 64}}
+    recurrent = {"heads": heads, "dim": 128, "vdim": 128}
+    stack, source = [], None
+    for index in range(layers):
+        if index % 2 == 0:
+            mixer = dict(attention)
+            if source is not None:
+                mixer["kv_from"], source = source, None
+            else:
+                source = index
+            stack.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": 4 * width}})
+        else:
+            stack.append({"type": "hgrn2", "mixer": dict(recurrent), "mlp": {"kind": "dense", "ff": 4 * width}})
+    return {"architecture": "Sanozen", "vocab": 32768, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "token_side": {"dim": 64}, "layers": stack, "max_positions": 8192}
+
+
+def qwen3_shape(width: int, layers: int = 4) -> dict:
+    """The closest existing model at equal size: Qwen3 layers of the same width and head count (a key/value head for
+    four heads) whose gated feed-forward has as many weights as the dense one of 4 width."""
+    heads = width // 128
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), intermediate_size=(8 * width // 3 + 127) // 128 * 128,
+                vocab_size=32768, max_position_embeddings=8192)
+
+
+KERNEL_CLASSES = (
+    ("products", ("gemm_", "library_mm", "gemm_heads")),
+    ("prompt attention", ("attention_prefill",)),
+    ("decode attention", ("attention_decode", "latent_attention")),
+    ("recurrence", ("gated_recurrence",)),
+    ("stream norm", ("add_rmsnorm", "add_layernorm")),
+    ("activation", ("silu_gate", "poly_norm")),
+)
+
+
+def kernel_class(name: str) -> str:
+    for label, prefixes in KERNEL_CLASSES:
+        if name.startswith(prefixes):
+            return label
+    return "other row-wise kernels"
+
+
+def timed_step(engine, slots, tokens) -> dict:
+    """One `Engine.step` with every launch timed on the device: microseconds and launches per class of kernel."""
+    from kidi_b200 import StepBatch
+    from kidi_b200.kernels import ops
+    with ops.time_launches() as timed:
+        engine.step(StepBatch(slots, tokens, None))
+    classes: dict = {}
+    for name, microseconds in timed.spans():
+        entry = classes.setdefault(kernel_class(name), {"us": 0.0, "launches": 0, "kernels": {}})
+        entry["us"] += microseconds
+        entry["launches"] += 1
+        kernel = entry["kernels"].setdefault(name.split(",")[0], [0, 0.0])
+        kernel[0] += 1
+        kernel[1] += microseconds
+    for entry in classes.values():
+        entry["us"] = round(entry["us"], 1)
+        entry["kernels"] = {name: [count, round(us, 1)] for name, (count, us) in entry["kernels"].items()}
+    return classes
+
+
+def class_work(design: str, config: dict, rows: int, context: int, decode: bool) -> dict:
+    """What each class of kernel has to do in one step, per the algorithm: ("flops" | "bytes", amount). Prompts:
+    `rows` tokens of one sequence from position 0; decoding: `rows` sequences of `context` tokens."""
+    work = {}
+    if design == "qwen3":
+        width, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+        heads, kv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+        weights = layers * (width * (heads + 2 * kv) * hd + heads * hd * width + 3 * width * inter) + config["vocab_size"] * width
+        norms, act_width = 2 * layers + 1, layers * inter * 3          # gate and up read, the product written
+        work["prompt attention"] = ("flops", layers * 4.0 * heads * hd * rows * (rows + 1) / 2)
+        work["decode attention"] = ("bytes", layers * rows * context * kv * hd * 2 * 2.0)
+    else:
+        width, layers = config["width"], config["layers"]
+        weights, norms, act_width, attention, cache, scan_flops, scan_bytes, state = config["vocab"] * width, 1, 0, 0.0, 0.0, 0.0, 0.0, 0.0
+        for layer in layers:
+            m, ff = layer["mixer"], layer["mlp"]["ff"] if layer["mlp"] else 0
+            weights += 2 * width * ff + 2 * width * config["token_side"]["dim"]
+            norms += 2 if ff else 1
+            act_width += 2 * ff
+            if layer["type"] == "latent_attention":
+                head = m["dim"] + m["rot_dim"]
+                weights += width * m["q_rank"] + m["q_rank"] * m["heads"] * head + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"] \
+                    + m["heads"] * m["vdim"] * width + (0 if "kv_from" in m else width * (m["kv_rank"] + m["rot_dim"]))
+                attention += 4.0 * m["heads"] * head * rows * (rows + 1) / 2       # values padded to the key width
+                cache += rows * context * (m["kv_rank"] + m["rot_dim"]) * 2.0
+            else:
+                weights += width * m["heads"] * (2 * m["dim"] + m["vdim"]) + m["heads"] * m["vdim"] * width
+                scan_flops += 4.0 * rows * m["heads"] * m["dim"] * m["vdim"]
+                scan_bytes += rows * m["heads"] * (2 * m["dim"] + 2 * m["vdim"]) * 2.0
+                state += 2.0 * m["heads"] * m["dim"] * m["vdim"] * 4
+        work["prompt attention"] = ("flops", attention)
+        work["decode attention"] = ("bytes", cache)
+        work["recurrence"] = ("bytes", scan_bytes + (rows if decode else 1) * state)
+    work["products"] = ("bytes", 2.0 * weights) if decode else ("flops", 2.0 * rows * weights)
+    work["stream norm"] = ("bytes", norms * rows * width * (4 + 4 + 2 + 2.0))
+    work["activation"] = ("bytes", rows * act_width * 2.0)
+    if decode:
+        work.pop("prompt attention")
+    else:
+        work.pop("decode attention")
+    return work
+
+
+def design_comparison(args) -> int:
+    """`--design sanozen`: prompts and decoding of a Sanozen stack beside Qwen3 layers of equal size, with every
+    class of kernel against its roofline."""
+    import torch
+    from kidi_b200 import Engine
+    from kidi_b200.sampling.sampler import Sampler
+
+    peak = peaks()
+    sampler = Sampler(args.seed)
+    batch, context, steps = args.batch or 8, 1024, args.steps or 64
+    sizes = []
+    for width in [int(value) for value in args.widths.split(",")]:
+        point = {"width": width}
+        for design, shape in (("sanozen", sanozen_shape(width, args.layers or 4)), ("qwen3", qwen3_shape(width, args.layers or 4))):
+            engine = Engine.from_config(shape, seed=args.seed, dtype="bfloat16", device="cuda:0",
+                                        max_tokens=max(batch * (context + steps + 64 + args.warmup), 4096))
+            prefill_ms = time_prefill(engine, args.seed)
+            prompts = draw_prompts(engine.vocab_size, batch, (context, context), args.seed)
+            run = time_decode(engine, sampler, prompts, steps, args.warmup, clocks=False, repeats=1)
+            slot = engine.acquire()
+            prompt = draw_prompts(engine.vocab_size, 1, (PREFILL_TOKENS, PREFILL_TOKENS), args.seed + 1)[0]
+            prompt_classes = timed_step(engine, [slot], [prompt])
+            engine.release(slot)
+            slots = [engine.acquire() for _ in range(batch)]
+            from kidi_b200 import StepBatch
+            engine.step(StepBatch(slots, prompts, None))
+            engine.step(StepBatch(slots, [[1]] * batch, None))           # every decode kernel is built and configured
+            decode_classes = timed_step(engine, slots, [[2]] * batch)
+            for used in slots:
+                engine.release(used)
+            for classes, decode in ((prompt_classes, False), (decode_classes, True)):
+                work = class_work(design, shape, batch if decode else PREFILL_TOKENS, context + 2, decode)
+                for label, entry in classes.items():
+                    if label in work and entry["us"] > 0:
+                        kind, amount = work[label]
+                        rate = amount / (entry["us"] * 1e-6)
+                        entry["roofline"] = kind
+                        entry["frac"] = round(rate / (peak["bf16_tflops"] * 1e12 if kind == "flops" else peak["hbm_gbs"] * 1e9), 4)
+            point[design] = {
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                "decode_tokens_per_s": round(run["tokens_per_s"], 1), "decode_ms_per_step": round(run["ms_per_step"], 4),
+                "decode_kernels_per_step": run["kernels_per_step"], "weight_bytes": engine.memory()["weight_bytes"],
+                "prompt_kernels": prompt_classes, "decode_kernels": decode_classes}
+            del engine
+            torch.cuda.empty_cache()
+        sizes.append(point)
+    print(json.dumps({
+        "metric": f"prefill and decode tokens/s of a Sanozen stack beside Qwen3 layers of equal size (bf16, "
+                  f"{args.layers or 4} layers, one {PREFILL_TOKENS}-token prompt; batch {batch} decoding at {context} tokens)",
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16", "impl": "ours",
+        "data": "synthetic: random weights from a seed, uniform token ids", "peaks": peak, "sizes": sizes,
+        "note": "kernel times: one step with a CUDA event behind every launch, queued behind a 20 ms head start so "
+                "that the device never waits for the host; frac: the class's algorithmic FLOPs or bytes over its "
+                "time, of the measured product peak or copy rate"}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--design", default="", choices=["", "sanozen"],
+                        help="sanozen: a Sanozen stack beside Qwen3 layers of equal size, kernel class by kernel class "
+                             "(the default workload is left as it is)")
+    parser.add_argument("--widths", default="2048,4096", help="model widths of --design runs")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=0, help="timed decode steps (default: the model's: 512 / 256)")
     parser.add_argument("--warmup", type=int, default=8)
@@ -308,6 +484,11 @@ def main() -> int:
                           "third_party' (empty submodules), and its Qwen3 is an INT8 bidirectional backbone "
                           "without cache, head or generation"}))
         return 0
+    if args.design and args.gpus == 1:
+        if args.warmup < 3:
+            print("bench.py needs --warmup >= 3")
+            return 2
+        return design_comparison(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is single-GPU by design (asked for {args.gpus})")
         return 2

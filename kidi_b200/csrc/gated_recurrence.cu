@@ -9,8 +9,9 @@
 // The recurrence is elementwise in S, so the columns v of a head's state are independent: a block takes 32
 // columns of one (sequence, head) and walks the sequence's rows of the step in order. Warp g of its eight owns the
 // state rows d = g R .. g R + R - 1 of those columns in registers (R = ceil(dim / 8)); the gates and queries of 16
-// tokens at a time are computed once a block into shared memory; the eight partial read-outs of a column meet in
-// shared memory and are added in the order of g. A token's result therefore depends on the sizes only: not on
+// tokens at a time are computed once a block into shared memory, a chunk ahead of the one being computed (its
+// projections are loaded into registers before the current chunk's tokens are walked, so their latency hides
+// behind the walk); the eight partial read-outs of a column meet in shared memory and are added in the order of g. A token's result therefore depends on the sizes only: not on
 // what else is in the step, nor on how the sequence was cut into steps. The read-out leaves the kernel
 // unnormalised (its columns lie in different blocks); the norm over vdim is a kernel of its own.
 #include "common.cuh"
@@ -31,25 +32,41 @@ struct GatedRecurrenceArgs {
 };
 
 namespace {
+// A load that stays where it is written: the compiler would otherwise move a chunk's loads down to their first
+// use, behind the walk over the chunk before it, and their latency would no longer hide behind that walk.
+__device__ __forceinline__ float load_here(const float* pointer) {
+    float value;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(value) : "l"(pointer));
+    return value;
+}
+__device__ __forceinline__ float load_here(const bf16* pointer) {
+    unsigned short bits;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(bits) : "l"(pointer));
+    return __uint_as_float((unsigned)bits << 16);
+}
+
 constexpr int GROUPS = 8;       // warps of a block: each owns a slice of the state's rows
 constexpr int COLUMNS = 32;     // state columns of a block: one a lane
 constexpr int CHUNK = 16;       // tokens whose gates are staged at a time
 
 template <typename T, int R>
 __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(GatedRecurrenceArgs a) {
-    extern __shared__ float shared[];
+    extern __shared__ __align__(16) float shared[];
+    constexpr int THREADS = GROUPS * COLUMNS;
+    constexpr int PADDED = GROUPS * R;                   // dim rounded up: rows beyond dim hold q = 0, f = 1
+    constexpr int GATES = (CHUNK * PADDED + THREADS - 1) / THREADS;     // (q, f) pairs a thread stages a chunk
+    constexpr int VALUES = CHUNK * COLUMNS / THREADS;
     const int seq = blockIdx.x, head = blockIdx.y;
     const int row0 = a.seq_row0[seq], count = a.seq_len[seq];
     if (count <= 0 || a.row_seq[row0] < 0) return;       // a padding sequence touches no state
     const int dim = a.dim, vdim = a.vdim;
-    constexpr int PADDED = GROUPS * R;                   // dim rounded up: rows beyond dim hold q = 0, f = 1
-    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int lane = threadIdx.x % COLUMNS, g = threadIdx.x / COLUMNS;
     const int v = blockIdx.z * COLUMNS + lane;
     const bool live = v < vdim;
-    float* qs = shared;                                  // [CHUNK][PADDED]
-    float* fs = qs + CHUNK * PADDED;                     // [CHUNK][PADDED]
-    float* vs = fs + CHUNK * PADDED;                     // [CHUNK][COLUMNS]
-    float* partial = vs + CHUNK * COLUMNS;               // [CHUNK][GROUPS][COLUMNS]
+    // two stages of (q, f, v) of CHUNK tokens, two of partial read-outs
+    float* stage = shared;                               // [2][CHUNK][2 * PADDED + COLUMNS]
+    constexpr int STAGE = CHUNK * (2 * PADDED + COLUMNS);
+    float* partials = shared + 2 * STAGE;                // [2][CHUNK][GROUPS][COLUMNS]
     float* state = a.state + ((long long)a.seq_slot[seq] * a.heads + head) * dim * vdim;
     float S[R];
 #pragma unroll
@@ -59,43 +76,95 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
     }
     const float* bias = a.f_bias + head * dim;
     const float* lower = a.lower + head * dim;
-    for (int t0 = 0; t0 < count; t0 += CHUNK) {
+    float raw_q[GATES], raw_f[GATES], raw_v[VALUES];
+
+    // the raw projections of the chunk that starts at token t0, into registers (all loads in flight together)
+    auto fetch = [&](int t0) {
         const int tokens = min(CHUNK, count - t0);
-        for (int index = threadIdx.x; index < tokens * PADDED; index += GROUPS * COLUMNS) {
-            const int t = index / PADDED, d = index - t * PADDED;
+#pragma unroll
+        for (int i = 0; i < GATES; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
+            raw_q[i] = raw_f[i] = 0.f;
+            if (t < tokens && d < dim) {
+                const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
+                raw_q[i] = load_here(row + head * dim + d);
+                raw_f[i] = load_here(row + (a.heads + head) * dim + d);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VALUES; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
+            const int column = blockIdx.z * COLUMNS + c;
+            raw_v[i] = 0.f;
+            if (t < tokens && column < vdim)
+                raw_v[i] = load_here((const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld + 2 * a.heads * dim + head * vdim + column);
+        }
+    };
+    // activations and gates of the fetched chunk, into a stage of shared memory
+    auto put = [&](float* target) {
+#pragma unroll
+        for (int i = 0; i < GATES; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
+            if (index >= CHUNK * PADDED) continue;
             float q = 0.f, f = 1.f;
             if (d < dim) {
-                const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
-                const float raw = to_float(row[head * dim + d]);
-                q = raw / (1.0f + expf(-raw));
-                const float gate = 1.0f / (1.0f + expf(-(to_float(row[(a.heads + head) * dim + d]) + bias[d])));
+                q = raw_q[i] / (1.0f + expf(-raw_q[i]));
+                const float gate = 1.0f / (1.0f + expf(-(raw_f[i] + bias[d])));
                 f = lower[d] + (1.0f - lower[d]) * gate;
             }
-            qs[index] = q;
-            fs[index] = f;
+            target[t * (2 * PADDED + COLUMNS) + d] = q;
+            target[t * (2 * PADDED + COLUMNS) + PADDED + d] = f;
         }
-        for (int index = threadIdx.x; index < tokens * COLUMNS; index += GROUPS * COLUMNS) {
-            const int t = index / COLUMNS, c = index - t * COLUMNS;
-            const int column = blockIdx.z * COLUMNS + c;
-            const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
-            vs[index] = column < vdim ? to_float(row[2 * a.heads * dim + head * vdim + column]) : 0.f;
-        }
-        __syncthreads();
-        for (int t = 0; t < tokens; ++t) {
-            const float value = vs[t * COLUMNS + lane];
-            const float* q = qs + t * PADDED + g * R;    // the same addresses for a whole warp: broadcasts
-            const float* f = fs + t * PADDED + g * R;
-            float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < R; ++j) {
-                const float s = f[j] * S[j] + (1.0f - f[j]) * value;
-                S[j] = s;
-                sum = fmaf(s, q[j], sum);
+        for (int i = 0; i < VALUES; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
+            target[t * (2 * PADDED + COLUMNS) + 2 * PADDED + c] = raw_v[i];
+        }
+    };
+
+    fetch(0);
+    put(stage);
+    __syncthreads();
+    int turn = 0;
+    for (int t0 = 0; t0 < count; t0 += CHUNK, turn ^= 1) {
+        const int tokens = min(CHUNK, count - t0);
+        const bool more = t0 + CHUNK < count;
+        if (more) fetch(t0 + CHUNK);                     // on their way while this chunk is computed
+        const float* current = stage + turn * STAGE;
+        float* partial = partials + turn * (CHUNK * GROUPS * COLUMNS);
+        for (int t = 0; t < tokens; ++t) {
+            const float* q = current + t * (2 * PADDED + COLUMNS) + g * R;   // one address a warp: broadcasts
+            const float* f = q + PADDED;
+            const float value = current[t * (2 * PADDED + COLUMNS) + 2 * PADDED + lane];
+            float sum = 0.f;
+            if constexpr (R % 4 == 0) {
+                float sums[4] = {0.f, 0.f, 0.f, 0.f};     // four chains instead of one of R links
+#pragma unroll
+                for (int j = 0; j < R; j += 4) {
+                    const float4 f4 = *reinterpret_cast<const float4*>(f + j), q4 = *reinterpret_cast<const float4*>(q + j);
+                    const float fj[4] = {f4.x, f4.y, f4.z, f4.w}, qj[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float s = fmaf(fj[e], S[j + e] - value, value);     // f S + (1 - f) v
+                        S[j + e] = s;
+                        sums[e] = fmaf(s, qj[e], sums[e]);
+                    }
+                }
+                sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < R; ++j) {
+                    const float s = fmaf(f[j], S[j] - value, value);                  // f S + (1 - f) v
+                    S[j] = s;
+                    sum = fmaf(s, q[j], sum);
+                }
             }
             partial[(t * GROUPS + g) * COLUMNS + lane] = sum;
         }
+        if (more) put(stage + (turn ^ 1) * STAGE);
         __syncthreads();
-        for (int index = threadIdx.x; index < tokens * COLUMNS; index += GROUPS * COLUMNS) {
+        // (the stage and the partials written next are the other ones; these are free again behind the next barrier)
+        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS) {
             const int t = index / COLUMNS, c = index - t * COLUMNS;
             const int column = blockIdx.z * COLUMNS + c;
             if (column >= vdim) continue;
@@ -104,8 +173,6 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
             for (int k = 0; k < GROUPS; ++k) total += partial[(t * GROUPS + k) * COLUMNS + c];
             ((T*)a.out)[(long long)(row0 + t0 + t) * a.ldo + head * vdim + column] = from_float<T>(total);
         }
-        // the next chunk's staging writes qs, fs and vs, which nobody reads any more; `partial` is written
-        // again only behind the next barrier
     }
 #pragma unroll
     for (int j = 0; j < R; ++j) {
@@ -116,7 +183,7 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
 
 template <typename T, int R>
 int launch(const GatedRecurrenceArgs& a, cudaStream_t stream) {
-    const size_t shared = (size_t)(2 * CHUNK * GROUPS * R + CHUNK * COLUMNS + CHUNK * GROUPS * COLUMNS) * sizeof(float);
+    const size_t shared = (size_t)2 * (CHUNK * (2 * GROUPS * R + COLUMNS) + CHUNK * GROUPS * COLUMNS) * sizeof(float);
     auto kernel = gated_recurrence_kernel<T, R>;
     if (shared > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);

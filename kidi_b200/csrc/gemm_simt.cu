@@ -119,3 +119,49 @@ KIDI_API int kidi_gemm_simt_batched(const void* x, int x_dtype, const void* w, i
 #undef KIDI_CASE
     return KIDI_REFUSED_DTYPE;
 }
+
+// The same batch of products for few rows (M <= 8): a warp computes y[0..M-1, n] of one product of the batch, its
+// lanes striding k; the weight row is read once for all M rows. A row's result depends on K only.
+namespace {
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(128)
+gemm_rows_batched_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int M, int N, int K,
+                         long long ldx, long long ldw, long long ldy, long long batch_x, long long batch_w,
+                         long long batch_y) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + warp;
+    if (n >= N) return;
+    x += blockIdx.y * batch_x;
+    w += blockIdx.y * batch_w + n * ldw;
+    y += blockIdx.y * batch_y;
+    float acc[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float weight = to_float(w[k]);
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+            if (m < M) acc[m] = fmaf(to_float(x[m * ldx + k]), weight, acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const float total = warp_sum(acc[m]);
+        if (lane == 0 && m < M) y[m * ldy + n] = from_float<TY>(total);
+    }
+}
+}  // namespace
+
+KIDI_API int kidi_gemm_rows_batched(const void* x, const void* w, void* y, int dtype, int M, int N, int K, long long ldx,
+                                    long long ldw, long long ldy, int batch, long long batch_x, long long batch_w,
+                                    long long batch_y, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || M > 8 || batch > 65535) return KIDI_REFUSED_SIZE;
+    dim3 grid((N + 3) / 4, batch);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(gemm_rows_batched_kernel<bf16, bf16, bf16>, grid, 128, 0, stream, (const bf16*)x, (const bf16*)w,
+                           (bf16*)y, M, N, K, ldx, ldw, ldy, batch_x, batch_w, batch_y);
+    if (dtype == KIDI_F32)
+        return kidi_launch(gemm_rows_batched_kernel<float, float, float>, grid, 128, 0, stream, (const float*)x,
+                           (const float*)w, (float*)y, M, N, K, ldx, ldw, ldy, batch_x, batch_w, batch_y);
+    return KIDI_REFUSED_DTYPE;
+}

@@ -255,10 +255,54 @@ __global__ void __launch_bounds__(128) latent_pack_kernel(LatentPackArgs a) {
     }
 }
 
+// The same in 16-byte pieces (bfloat16; every width a multiple of 8, rows 16-byte aligned): a piece never
+// straddles two parts of a head, and a rotated piece holds four whole pairs.
+__global__ void __launch_bounds__(256) latent_pack_bf16x8_kernel(LatentPackArgs a) {
+    const int row = blockIdx.x;
+    const int D = a.dim + a.rot_dim, half = a.rotary_dims / 2;
+    const int position = a.row_seq[row] < 0 ? 0 : a.row_pos[row];
+    const float* cosine = a.cos_table + (long long)position * half;
+    const float* sine = a.sin_table + (long long)position * half;
+    const bf16* q = (const bf16*)a.q + row * a.ldq;
+    const bf16* latent = (const bf16*)a.latent + row * a.ldl;
+    const bf16* unfolded = (const bf16*)a.unfolded + row * a.ldu;
+    bf16* packed = (bf16*)a.packed + row * a.ldp;
+    const int per_head = D / 8, per_section = a.heads * per_head;
+    for (int piece = threadIdx.x; piece < 3 * per_section; piece += 256) {
+        const int section = piece / per_section, within = piece - section * per_section;
+        const int head = within / per_head, c = (within - head * per_head) * 8;
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (section == 0) {
+            value = *reinterpret_cast<const uint4*>(q + head * D + c);
+            if (c >= a.dim && c < a.dim + a.rotary_dims) {
+                const int i = (c - a.dim) >> 1;
+                const float4 cs = *reinterpret_cast<const float4*>(cosine + i), sn = *reinterpret_cast<const float4*>(sine + i);
+                const float c4[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
+                __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&value);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 uv = __bfloat1622float2(pairs[e]);
+                    pairs[e] = __floats2bfloat162_rn(uv.x * c4[e] - uv.y * s4[e], uv.y * c4[e] + uv.x * s4[e]);
+                }
+            }
+        } else if (section == 1) {
+            value = c < a.dim ? *reinterpret_cast<const uint4*>(unfolded + head * a.dim + c)
+                              : *reinterpret_cast<const uint4*>(latent + a.rank + c - a.dim);
+        } else if (c < a.vdim) {
+            value = *reinterpret_cast<const uint4*>(unfolded + a.heads * a.dim + head * a.vdim + c);
+        }
+        *reinterpret_cast<uint4*>(packed + (long long)piece * 8) = value;
+    }
+}
+
 KIDI_API int kidi_latent_pack(const LatentPackArgs* args, int dtype, cudaStream_t stream) {
     const LatentPackArgs& a = *args;
     if (a.rows <= 0) return 0;
     if (a.heads <= 0 || a.vdim > a.dim + a.rot_dim || a.rotary_dims > a.rot_dim || (a.rotary_dims & 1)) return KIDI_REFUSED_SIZE;
+    const bool pieces = dtype == KIDI_BF16 && !((a.dim | a.rot_dim | a.vdim | a.rank | a.rotary_dims) & 7) &&
+                        !((a.ldq | a.ldl | a.ldu | a.ldp) & 7) && !(((uintptr_t)a.q | (uintptr_t)a.latent |
+                        (uintptr_t)a.unfolded | (uintptr_t)a.packed | (uintptr_t)a.cos_table | (uintptr_t)a.sin_table) & 15);
+    if (pieces) return kidi_launch(latent_pack_bf16x8_kernel, a.rows, 256, 0, stream, a);
     if (dtype == KIDI_F32) return kidi_launch(latent_pack_kernel<float>, a.rows, 128, 0, stream, a);
     if (dtype == KIDI_BF16) return kidi_launch(latent_pack_kernel<bf16>, a.rows, 128, 0, stream, a);
     return KIDI_REFUSED_DTYPE;
@@ -297,13 +341,13 @@ KIDI_API int kidi_latent_gather(const void* cache, const CacheGeometry* geometry
 
 // ---------------------------------------------------------------------------
 // The folded form on the tensor cores (bfloat16; rank and rot_dim multiples of 16, rank <= 512, pages of 64
-// tokens, no window). A block of four warps takes one row of the step, a tile of up to 16 of its heads and a share
+// tokens, no window). A block of eight warps takes one row of the step, a tile of up to 16 of its heads and a share
 // of its sequence's pages. A page [64 tokens, W = rank + rot_dim] is copied to shared memory once (cp.async) and
 // serves as the keys of S = Q K^T (all W columns) and, its first `rank` columns, as the values of O += P C: the
-// cached rows are read once for all heads of the tile. Warp w computes the scores of the page's tokens 16w..16w+15
-// for the 16 heads (`mma.sync` m16n8k16, fragments by `ldmatrix`), the warps exchange row maxima and sums through
+// cached rows are read once for all heads of the tile. Warp w of eight computes the scores of the page's tokens
+// 8w..8w+7 for the 16 heads (`mma.sync` m16n8k16, fragments by `ldmatrix`), the warps exchange row maxima and sums through
 // shared memory (online softmax in 32-bit), P goes to shared memory in bfloat16, and warp w accumulates the output
-// columns of its n-tiles (tile i belongs to warp i mod 4) with the page as a transposed B operand
+// columns of its n-tiles (tile i belongs to warp i mod 8) with the page as a transposed B operand
 // (`ldmatrix.trans`). Every block leaves (O, max, sum) of its share in a workspace; `latent_combine` merges the
 // shares of a (row, head) in their order.
 struct LatentDecodeArgs {
@@ -321,6 +365,8 @@ struct LatentDecodeArgs {
     long long ldo;
     int rows, heads, rank, rot_dim, splits;
     float scale;
+    int splits_are_long;    // > 0: a share holds several pages: worth a second page buffer even at one block an
+                            // SM; < 0: one page buffer whatever the sizes
 };
 
 namespace {
@@ -347,17 +393,19 @@ __device__ __forceinline__ void copy_async_16(unsigned destination, const void* 
 
 constexpr int PAGE = 64;
 
-template <int TILES>   // output n-tiles (8 columns) a warp owns at most: rank <= 32 * TILES
-__global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) {
+constexpr int WARPS = 8;
+
+template <int TILES, int BUFFERS>   // output n-tiles (8 columns) a warp owns at most: rank <= 64 * TILES; page buffers
+__global__ void __launch_bounds__(32 * WARPS) latent_decode_kernel(LatentDecodeArgs a) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int row = blockIdx.x, head0 = blockIdx.y * 16, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int W = a.rank + a.rot_dim, stride = W + 8;      // padded rows: ldmatrix without bank conflicts
     bf16* Qs = reinterpret_cast<bf16*>(raw);                // [16][stride]
-    bf16* Ks = Qs + 16 * stride;                            // [64][stride]
-    bf16* Ps = Ks + PAGE * stride;                          // [16][PAGE + 8]
-    float* wmax = reinterpret_cast<float*>(Ps + 16 * (PAGE + 8));   // [4][16]
-    float* wsum = wmax + 64;                                // [4][16]
+    bf16* pages_at = Qs + 16 * stride;                      // [BUFFERS][64][stride]
+    bf16* Ps = pages_at + BUFFERS * PAGE * stride;          // [16][PAGE + 8]
+    float* wmax = reinterpret_cast<float*>(Ps + 16 * (PAGE + 8));   // [WARPS][16]
+    float* wsum = wmax + WARPS * 16;                        // [WARPS][16]
     const int heads_here = min(16, a.heads - head0);
     float* part_o = a.part_o + (((long long)row * a.splits + split) * a.heads + head0) * a.rank;
     float* part_stat = a.part_stat + (((long long)row * a.splits + split) * a.heads + head0) * 2;
@@ -378,51 +426,65 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) 
         }
         return;
     }
-    // the tile's queries, zero rows beyond the heads
+    // the tile's queries (zero rows beyond the heads) travel with the first page
     const bf16* q = (const bf16*)a.folded + row * a.ldf + (long long)head0 * W;
-    const int chunks = W / 8;                               // 16-byte pieces of a row
-    for (int index = threadIdx.x; index < 16 * chunks; index += 128) {
-        const int h = index / chunks, c = (index - h * chunks) * 8;
-        uint4 value = make_uint4(0u, 0u, 0u, 0u);
-        if (h < heads_here) value = *reinterpret_cast<const uint4*>(q + (long long)h * W + c);
-        *reinterpret_cast<uint4*>(Qs + h * stride + c) = value;
-    }
+    for (int h = warp; h < 16; h += WARPS)
+        for (int c = lane * 8; c < W; c += 256) {
+            if (h < heads_here) copy_async_16(shared_address(Qs + h * stride + c), q + (long long)h * W + c);
+            else *reinterpret_cast<uint4*>(Qs + h * stride + c) = make_uint4(0u, 0u, 0u, 0u);
+        }
     float o[TILES][4];
 #pragma unroll
     for (int i = 0; i < TILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float best[2] = {-INFINITY, -INFINITY}, denom[2] = {0.f, 0.f};   // of rows g and g + 8
     const int n_tiles = a.rank / 8;
-    for (int page_index = first_page; page_index < last_page; ++page_index) {
+    // a page of the cache into one of the buffers, 16 bytes a copy
+    auto copy_page = [&](int page_index, bf16* target) {
         const int page = a.table[(long long)slot * a.pages_per_seq + page_index];
         const bf16* source = (const bf16*)a.cache + (long long)page * PAGE * W;
-        __syncthreads();                                    // the last page's products have read Ks and Ps
-        for (int index = threadIdx.x; index < PAGE * chunks; index += 128) {
-            const int r = index / chunks, c = (index - r * chunks) * 8;
-            copy_async_16(shared_address(Ks + r * stride + c), source + (long long)r * W + c);
-        }
+        for (int r = warp; r < PAGE; r += WARPS)
+            for (int c = lane * 8; c < W; c += 256)
+                copy_async_16(shared_address(target + r * stride + c), source + (long long)r * W + c);
         asm volatile("cp.async.commit_group;");
+    };
+    copy_page(first_page, pages_at);
+    for (int page_index = first_page; page_index < last_page; ++page_index) {
+        const bf16* Ks = pages_at + ((page_index - first_page) % BUFFERS) * PAGE * stride;
         asm volatile("cp.async.wait_group 0;");
-        __syncthreads();
-        // scores of tokens 16 warp .. 16 warp + 15 against the 16 heads
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        for (int k0 = 0; k0 < W; k0 += 16) {
-            unsigned qa[4], kb[4];
-            ldmatrix_x4(qa, shared_address(Qs + (lane & 15) * stride + k0 + (lane >> 4) * 8));
-            const int mi = lane >> 3;
-            ldmatrix_x4(kb, shared_address(Ks + (16 * warp + (mi >> 1) * 8 + (lane & 7)) * stride + k0 + (mi & 1) * 8));
-            mma_bf16(s[0], qa, kb[0], kb[1]);
-            mma_bf16(s[1], qa, kb[2], kb[3]);
+        __syncthreads();                                    // this page has landed; the last page's products are done
+        if (BUFFERS > 1) {
+            if (page_index + 1 < last_page)                 // the next page travels while this one is computed
+                copy_page(page_index + 1, pages_at + ((page_index + 1 - first_page) % BUFFERS) * PAGE * stride);
         }
-        const int token0 = page_index * PAGE + 16 * warp + 2 * t;
+        // scores of tokens 8 warp .. 8 warp + 7 against the 16 heads: two k-steps a round, each with an
+        // accumulator of its own, so that neither the loads nor the products wait for one another
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s_other[4] = {0.f, 0.f, 0.f, 0.f};
+        const unsigned q_at = shared_address(Qs + (lane & 15) * stride + (lane >> 4) * 8);
+        const unsigned k_at = shared_address(Ks + (8 * warp + (lane & 7)) * stride + (lane >> 3) * 8);
+        int k0 = 0;
+#pragma unroll 2
+        for (; k0 + 32 <= W; k0 += 32) {
+            unsigned qa[4], qb[4], kb[4];
+            ldmatrix_x4(kb, k_at + k0 * 2);                 // (k0..7, 8..15, 16..23, 24..31) of the warp's 8 tokens
+            ldmatrix_x4(qa, q_at + k0 * 2);
+            ldmatrix_x4(qb, q_at + (k0 + 16) * 2);
+            mma_bf16(s, qa, kb[0], kb[1]);
+            mma_bf16(s_other, qb, kb[2], kb[3]);
+        }
+        if (k0 < W) {                                       // a last k-step of 16: the upper two matrices are re-read
+            unsigned qa[4], kb[4];
+            ldmatrix_x4(kb, shared_address(Ks + (8 * warp + (lane & 7)) * stride + k0 + ((lane >> 3) & 1) * 8));
+            ldmatrix_x4(qa, q_at + k0 * 2);
+            mma_bf16(s, qa, kb[0], kb[1]);
+        }
+        const int token0 = page_index * PAGE + 8 * warp + 2 * t;
         float top[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int token = token0 + 8 * j + (e & 1);
-                s[j][e] = token <= position ? s[j][e] * a.scale : -INFINITY;
-                top[e >> 1] = fmaxf(top[e >> 1], s[j][e]);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int token = token0 + (e & 1);
+            s[e] = token <= position ? (s[e] + s_other[e]) * a.scale : -INFINITY;
+            top[e >> 1] = fmaxf(top[e >> 1], s[e]);
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             top[r] = fmaxf(top[r], __shfl_xor_sync(0xffffffffu, top[r], 1));
@@ -434,19 +496,20 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) 
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int h = g + 8 * r;
-            const float tile = fmaxf(fmaxf(wmax[h], wmax[16 + h]), fmaxf(wmax[32 + h], wmax[48 + h]));
+            float tile = wmax[h];
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) tile = fmaxf(tile, wmax[w * 16 + h]);
             next[r] = fmaxf(best[r], tile);                 // finite: the page holds a token at or before the position
             keep[r] = expf(best[r] - next[r]);              // 0 on the first page
         }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        {
             float p[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                p[e] = expf(s[j][e] - next[e >> 1]);
+                p[e] = expf(s[e] - next[e >> 1]);
                 sum[e >> 1] += p[e];
             }
-            const int column = 16 * warp + 8 * j + 2 * t;
+            const int column = 8 * warp + 2 * t;
             *reinterpret_cast<__nv_bfloat162*>(Ps + g * (PAGE + 8) + column) = __floats2bfloat162_rn(p[0], p[1]);
             *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * (PAGE + 8) + column) = __floats2bfloat162_rn(p[2], p[3]);
         }
@@ -460,41 +523,53 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) 
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int h = g + 8 * r;
-            denom[r] = denom[r] * keep[r] + ((wsum[h] + wsum[16 + h]) + (wsum[32 + h] + wsum[48 + h]));
+            float total = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) total += wsum[w * 16 + h];
+            denom[r] = denom[r] * keep[r] + total;
             best[r] = next[r];
         }
-        // O = O * keep + P C over this warp's n-tiles
+        // O = O * keep + P C over this warp's n-tiles (tile n belongs to warp n mod WARPS)
         unsigned pa[4][4];
 #pragma unroll
         for (int k = 0; k < 4; ++k)
             ldmatrix_x4(pa[k], shared_address(Ps + (lane & 15) * (PAGE + 8) + 16 * k + (lane >> 4) * 8));
 #pragma unroll
-        for (int i = 0; i < TILES; i += 2) {                // two n-tiles a ldmatrix: tiles n and n + 4 of this warp
-            const int n_first = warp + 4 * i, n_second = warp + 4 * (i + 1);
-            if (n_first >= n_tiles) break;
-            o[i][0] *= keep[0]; o[i][1] *= keep[0]; o[i][2] *= keep[1]; o[i][3] *= keep[1];
-            o[i + 1][0] *= keep[0]; o[i + 1][1] *= keep[0]; o[i + 1][2] *= keep[1]; o[i + 1][3] *= keep[1];
-            const bool both = n_second < n_tiles;
-            const int mi = lane >> 3;
-            const int column = ((mi >> 1) && both ? n_second : n_first) * 8;
+        for (int i = 0; i < TILES; i += 2) {                // two n-tiles a ldmatrix
+            const int n_first = warp + WARPS * i, n_second = warp + WARPS * (i + 1);
+            if (n_first < n_tiles) {
+                o[i][0] *= keep[0]; o[i][1] *= keep[0]; o[i][2] *= keep[1]; o[i][3] *= keep[1];
+                o[i + 1][0] *= keep[0]; o[i + 1][1] *= keep[0]; o[i + 1][2] *= keep[1]; o[i + 1][3] *= keep[1];
+                const bool both = n_second < n_tiles;
+                const int mi = lane >> 3;
+                const int column = ((mi >> 1) && both ? n_second : n_first) * 8;
+                unsigned cb[4][4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                unsigned cb[4];
-                ldmatrix_x4_trans(cb, shared_address(Ks + (16 * k + (mi & 1) * 8 + (lane & 7)) * stride + column));
-                mma_bf16(o[i], pa[k], cb[0], cb[1]);
-                if (both) mma_bf16(o[i + 1], pa[k], cb[2], cb[3]);
+                for (int k = 0; k < 4; ++k)
+                    ldmatrix_x4_trans(cb[k], shared_address(Ks + (16 * k + (mi & 1) * 8 + (lane & 7)) * stride + column));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mma_bf16(o[i], pa[k], cb[k][0], cb[k][1]);
+                    if (both) mma_bf16(o[i + 1], pa[k], cb[k][2], cb[k][3]);
+                }
             }
+        }
+        if (BUFFERS == 1 && page_index + 1 < last_page) {
+            __syncthreads();                                // one buffer: the next page may only be copied now
+            copy_page(page_index + 1, pages_at);
         }
     }
     // this share's result
 #pragma unroll
     for (int i = 0; i < TILES; ++i) {
-        const int n = warp + 4 * i;
-        if (n >= n_tiles) break;
-        const int column = n * 8 + 2 * t;
-        if (g < heads_here) *reinterpret_cast<float2*>(part_o + (long long)g * a.rank + column) = make_float2(o[i][0], o[i][1]);
-        if (g + 8 < heads_here)
-            *reinterpret_cast<float2*>(part_o + (long long)(g + 8) * a.rank + column) = make_float2(o[i][2], o[i][3]);
+        const int n = warp + WARPS * i;
+        if (n < n_tiles) {
+            const int column = n * 8 + 2 * t;
+            if (g < heads_here)
+                *reinterpret_cast<float2*>(part_o + (long long)g * a.rank + column) = make_float2(o[i][0], o[i][1]);
+            if (g + 8 < heads_here)
+                *reinterpret_cast<float2*>(part_o + (long long)(g + 8) * a.rank + column) = make_float2(o[i][2], o[i][3]);
+        }
     }
     if (warp == 0 && t == 0) {
         if (g < heads_here) { part_stat[g * 2] = best[0]; part_stat[g * 2 + 1] = denom[0]; }
@@ -530,19 +605,29 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(LatentDecodeArgs a)
     }
 }
 
-template <int TILES>
-int launch_decode(const LatentDecodeArgs& a, cudaStream_t stream) {
-    const int W = a.rank + a.rot_dim;
-    const size_t shared = (size_t)(16 + PAGE) * (W + 8) * 2 + 16 * (PAGE + 8) * 2 + 128 * sizeof(float);
-    auto kernel = latent_decode_kernel<TILES>;
+template <int TILES, int BUFFERS>
+int launch_decode_form(const LatentDecodeArgs& a, size_t shared, cudaStream_t stream) {
+    auto kernel = latent_decode_kernel<TILES, BUFFERS>;
     if (shared > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
     dim3 grid(a.rows, (a.heads + 15) / 16, a.splits);
-    const int status = kidi_launch(kernel, grid, 128, shared, stream, a);
+    const int status = kidi_launch(kernel, grid, 32 * WARPS, shared, stream, a);
     if (status) return status;
     return kidi_launch(latent_combine_kernel, dim3(a.rows, a.heads), 128, 0, stream, a);
+}
+
+template <int TILES>
+int launch_decode(const LatentDecodeArgs& a, cudaStream_t stream) {
+    const int W = a.rank + a.rot_dim;
+    const size_t rest = (size_t)16 * (W + 8) * 2 + 16 * (PAGE + 8) * 2 + 2 * WARPS * 16 * sizeof(float);
+    const size_t page = (size_t)PAGE * (W + 8) * 2;
+    // two page buffers (the next page is copied while this one is computed) where they leave room for two blocks
+    // an SM or the share has several pages anyway; else one
+    if (a.splits_are_long >= 0 && rest + 2 * page <= 110 * 1024) return launch_decode_form<TILES, 2>(a, rest + 2 * page, stream);
+    if (rest + 2 * page <= 220 * 1024 && a.splits_are_long > 0) return launch_decode_form<TILES, 2>(a, rest + 2 * page, stream);
+    return launch_decode_form<TILES, 1>(a, rest + page, stream);
 }
 }  // namespace
 
@@ -558,7 +643,7 @@ KIDI_API int kidi_latent_decode(const LatentDecodeArgs* args, cudaStream_t strea
         (a.rot_dim & 15) || a.rank > 512 || a.rot_dim < 0 || a.rank + a.rot_dim > 1024 || (a.ldf & 7) ||
         ((uintptr_t)a.folded & 15) || ((uintptr_t)a.cache & 15))
         return KIDI_REFUSED_SIZE;
-    if (a.rank <= 128) return launch_decode<4>(a, stream);
-    if (a.rank <= 256) return launch_decode<8>(a, stream);
-    return launch_decode<16>(a, stream);
+    if (a.rank <= 128) return launch_decode<2>(a, stream);
+    if (a.rank <= 256) return launch_decode<4>(a, stream);
+    return launch_decode<8>(a, stream);
 }

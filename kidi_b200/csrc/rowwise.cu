@@ -101,6 +101,46 @@ poly_norm_kernel(const T* __restrict__ z, T* __restrict__ out, const float* __re
     }
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: 16 bytes a load (the second pass finds the row in
+// the caches). The sums are added in another order than above, fixed by the width.
+__global__ void __launch_bounds__(ROW_THREADS)
+poly_norm_bf16x8_kernel(const bf16* __restrict__ z, bf16* __restrict__ out, const float* __restrict__ coefficients,
+                        int width, float eps) {
+    __shared__ float scratch[32];
+    const long long row = blockIdx.x;
+    const uint4* source = reinterpret_cast<const uint4*>(z + row * width);
+    const int pieces = width >> 3;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < pieces; i += ROW_THREADS) {
+        const uint4 piece = source[i];
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&piece);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 v = __bfloat1622float2(pairs[e]);
+            const float x2 = v.x * v.x, y2 = v.y * v.y, x3 = x2 * v.x, y3 = y2 * v.y;
+            s2 += x2 + y2;
+            s4 = fmaf(x2, x2, fmaf(y2, y2, s4));
+            s6 = fmaf(x3, x3, fmaf(y3, y3, s6));
+        }
+    }
+    const float r1 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s2, scratch) / (float)width + eps);
+    const float r2 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s4, scratch) / (float)width + eps);
+    const float r3 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s6, scratch) / (float)width + eps);
+    const float a = coefficients[0] * r1, b = coefficients[1] * r2, c3 = coefficients[2] * r3, e0 = coefficients[3];
+    uint4* target = reinterpret_cast<uint4*>(out + row * width);
+    for (int i = threadIdx.x; i < pieces; i += ROW_THREADS) {
+        uint4 piece = source[i];
+        __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&piece);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 v = __bfloat1622float2(pairs[e]);
+            pairs[e] = __floats2bfloat162_rn(fmaf(fmaf(fmaf(c3, v.x, b), v.x, a), v.x, e0),
+                                             fmaf(fmaf(fmaf(c3, v.y, b), v.y, a), v.y, e0));
+        }
+        target[i] = piece;
+    }
+}
+
 // ---------------------------------------------------------------- gate of a per-layer token input
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -216,9 +256,13 @@ KIDI_API int kidi_poly_norm(const void* z, void* out, int dtype, const float* co
     if (dtype == KIDI_F32)
         return kidi_launch(poly_norm_kernel<float>, rows, ROW_THREADS, 0, stream, (const float*)z, (float*)out,
                            coefficients, width, eps);
-    if (dtype == KIDI_BF16)
+    if (dtype == KIDI_BF16) {
+        if (!(width & 7) && !((uintptr_t)z & 15) && !((uintptr_t)out & 15))
+            return kidi_launch(poly_norm_bf16x8_kernel, rows, ROW_THREADS, 0, stream, (const bf16*)z, (bf16*)out,
+                               coefficients, width, eps);
         return kidi_launch(poly_norm_kernel<bf16>, rows, ROW_THREADS, 0, stream, (const bf16*)z, (bf16*)out,
                            coefficients, width, eps);
+    }
     return KIDI_REFUSED_DTYPE;
 }
 

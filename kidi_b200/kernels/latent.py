@@ -7,6 +7,7 @@ latent, rotates the shared key part and the queries' rotated parts and writes th
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -33,6 +34,8 @@ class AttentionArgs(ctypes.Structure):
 
 
 _library = None
+# KIDI_B200_LATENT_PAGE_BUFFERS: 1 or 2 page buffers in the tensor-core kernel whatever the sizes (default: chosen)
+PAGE_BUFFERS = int(os.environ.get("KIDI_B200_LATENT_PAGE_BUFFERS", "0"))
 
 
 def library():
@@ -150,7 +153,8 @@ class DecodeArgs(ctypes.Structure):
     _fields_ = [("folded", c_void_p), ("ldf", c_longlong), ("cache", c_void_p), ("table", c_void_p),
                 ("pages_per_seq", c_int), ("row_seq", c_void_p), ("row_pos", c_void_p), ("seq_slot", c_void_p),
                 ("part_o", c_void_p), ("part_stat", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("rows", c_int),
-                ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("scale", c_float)]
+                ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("scale", c_float),
+                ("splits_are_long", c_int)]
 
 
 def tensor_core_fits(dtype: torch.dtype, rank: int, rot_dim: int, window, kv_view) -> bool:
@@ -162,11 +166,12 @@ def tensor_core_fits(dtype: torch.dtype, rank: int, rot_dim: int, window, kv_vie
 
 
 def decode_splits(rows: int, heads: int, longest: int, device: torch.device) -> int:
-    """How many blocks share a sequence's pages: as many as fill the GPU about twice, at most one a page."""
+    """How many blocks share a sequence's pages: as many as fill the GPU once (every share costs a trip of its
+    partial result through the workspace), at most one a page."""
     from .attention import sm_count
     pages = max(1, -(-longest // 64))
     tiles = -(-heads // 16)
-    return max(1, min(pages, (2 * sm_count(device)) // max(1, rows * tiles)))
+    return max(1, min(pages, sm_count(device) // max(1, rows * tiles)))
 
 
 def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads: int, rank: int, rot_dim: int,
@@ -187,5 +192,6 @@ def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads
                       kv_view.table.shape[1], tables.row_seq.data_ptr(), tables.row_pos.data_ptr(),
                       tables.seq_slot.data_ptr(), workspace.data_ptr(),
                       workspace.data_ptr() + rows * splits * heads * rank * 4, out.data_ptr(), out.stride(0), rows,
-                      heads, rank, rot_dim, splits, float(scale))
+                      heads, rank, rot_dim, splits, float(scale),
+                      -1 if PAGE_BUFFERS == 1 else 1 if PAGE_BUFFERS == 2 or -(-ctx.plan.max_total // 64) > splits else 0)
     _check(library().kidi_latent_decode(ctypes.byref(args), ops._stream()), f"latent_attention[mma.sync, {splits} shares]", 2)

@@ -66,9 +66,50 @@ class record_launches:
 
 
 def note(what: str) -> None:
-    """Records work that is not one of this package's kernels (a vendor-library product)."""
+    """Records work that is not one of this package's kernels (a vendor-library product), after it was queued."""
     if _launch_log is not None:
         _launch_log.append(what)
+    if _timed is not None:
+        _timed.mark(what)
+
+
+_timed = None
+
+
+class time_launches:
+    """Times the kernels of the launches made while it is open, one by one, on the device: a CUDA event is recorded
+    behind every launch, and a launch's time is the span since the event before it. So that the spans hold no idle
+    time of a device waiting for the host, the stream is first kept busy for `head_start_ms` (a spin kernel of the
+    tensor library) while the host queues the launches behind it. `with time_launches() as timed: ...` then
+    `timed.spans()` -> [(name, microseconds)] in launch order (it synchronises)."""
+
+    def __init__(self, head_start_ms: float = 20.0):
+        self.head_start_ms = head_start_ms
+        self.names, self.events = [], []
+
+    def mark(self, what: str) -> None:
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        self.names.append(what)
+        self.events.append(event)
+
+    def __enter__(self) -> "time_launches":
+        global _timed
+        self._outer, _timed = _timed, self
+        torch.cuda.synchronize()
+        if self.head_start_ms > 0:
+            torch.cuda._sleep(int(self.head_start_ms * 1.5e6))     # cycles; the clock is between 1 and 2 GHz
+        self.mark("(start)")
+        return self
+
+    def __exit__(self, *exc) -> None:
+        global _timed
+        _timed = self._outer
+
+    def spans(self) -> list:
+        torch.cuda.synchronize()
+        return [(name, 1e3 * before.elapsed_time(after))
+                for name, before, after in zip(self.names[1:], self.events[:-1], self.events[1:])]
 
 
 def _check(status: int, what: str, launches: int = 1) -> None:
@@ -77,6 +118,8 @@ def _check(status: int, what: str, launches: int = 1) -> None:
         launch_count += launches
         if _launch_log is not None:
             _launch_log.append(what)
+        if _timed is not None:
+            _timed.mark(what)
         return
     if status == -2:
         raise unsupported(f"{what}: this combination of element types is not compiled")
@@ -126,6 +169,10 @@ def core():
         lib.kidi_gemm_simt_batched.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                c_longlong, c_longlong, c_longlong, c_int, c_longlong, c_longlong,
                                                c_longlong, c_void_p]
+        lib.kidi_gemm_rows_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+                                               c_longlong, c_longlong, c_int, c_longlong, c_longlong, c_longlong,
+                                               c_void_p]
+        lib.kidi_gemm_rows_batched.restype = c_int
         for name in ("kidi_add_layernorm", "kidi_rms_rows", "kidi_poly_norm", "kidi_token_gate", "kidi_add_normed_mix",
                      "kidi_add_cast", "kidi_gemm_simt_batched"):
             getattr(lib, name).restype = c_int
@@ -337,6 +384,12 @@ def gemm_heads(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torc
     N = weight.shape[1]
     if weight.shape != (heads, N, K) or out.shape != (rows, heads, N):
         raise invalid_argument("gemm_heads: the shapes do not fit")
+    if rows <= 8 and x.dtype == torch.bfloat16 and weight.dtype == x.dtype and out.dtype == x.dtype:
+        # few rows of the bfloat16 engine (decoding): a warp an output feature, the weights read once
+        _check(core().kidi_gemm_rows_batched(_ptr(x), _ptr(weight), _ptr(out), dtype_code(x.dtype), rows, N, K,
+                                             x.stride(0), K, out.stride(0), heads, x.stride(1), N * K, out.stride(1),
+                                             _stream()), "gemm_heads[rows]")
+        return out
     _check(core().kidi_gemm_simt_batched(_ptr(x), dtype_code(x.dtype), _ptr(weight), dtype_code(weight.dtype), _ptr(out),
                                          dtype_code(out.dtype), rows, N, K, x.stride(0), K, out.stride(0), heads,
                                          x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")

@@ -76,7 +76,6 @@ class Linear:
             return tcgen05.gemm(x, weight, out_dtype, out=out, bias=bias)
         if weight.shape[1] % 8 or x.stride(0) % 8:  # the library wants 16-byte rows; keep odd widths exact
             return ops.gemm_simt(x, weight, out_dtype, out=out, bias=bias)
-        ops.note("library_mm")
         if out is not None:
             result = torch.mm(x, weight.t(), out_dtype=out_dtype, out=out) if out_dtype != x.dtype else \
                 torch.mm(x, weight.t(), out=out)
@@ -84,4 +83,5 @@ class Linear:
             result = torch.mm(x, weight.t(), out_dtype=out_dtype)
         else:
             result = torch.mm(x, weight.t())
+        ops.note("library_mm")
         return ops.add_bias(result, bias) if bias is not None else result
