@@ -29,30 +29,43 @@ struct GatedRecurrenceArgs {
     const int* seq_row0;   // [seqs]
     const int* seq_len;    // [seqs]
     int seqs, heads, dim, vdim;
+    int narrow_blocks;     // the step brings many tokens a sequence: blocks of 16 columns when there are few blocks
 };
 
 namespace {
-// A load that stays where it is written: the compiler would otherwise move a chunk's loads down to their first
-// use, behind the walk over the chunk before it, and their latency would no longer hide behind that walk.
-__device__ __forceinline__ float load_here(const float* pointer) {
-    float value;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(value) : "l"(pointer));
-    return value;
-}
-__device__ __forceinline__ float load_here(const bf16* pointer) {
-    unsigned short bits;
-    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(bits) : "l"(pointer));
-    return __uint_as_float((unsigned)bits << 16);
-}
+// A load that stays where it is written and hands back the bits as they are. The compiler would otherwise move a
+// chunk's loads down to their first use, behind the walk over the chunk before it; and a conversion right behind a
+// load makes the warp wait for it there, load after load. So a chunk's loads are issued together, their bits wait
+// in registers, and they are converted where they are used.
+template <typename T> struct Raw;
+template <> struct Raw<float> {
+    typedef float type;
+    static __device__ __forceinline__ type load(const float* pointer) {
+        float value;
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(value) : "l"(pointer));
+        return value;
+    }
+    static __device__ __forceinline__ float value(type bits) { return bits; }
+};
+template <> struct Raw<bf16> {
+    typedef unsigned short type;
+    static __device__ __forceinline__ type load(const bf16* pointer) {
+        unsigned short bits;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(bits) : "l"(pointer));
+        return bits;
+    }
+    static __device__ __forceinline__ float value(type bits) { return __uint_as_float((unsigned)bits << 16); }
+};
 
-constexpr int GROUPS = 8;       // warps of a block: each owns a slice of the state's rows
-constexpr int COLUMNS = 32;     // state columns of a block: one a lane
+constexpr int THREADS = 256;
 constexpr int CHUNK = 16;       // tokens whose gates are staged at a time
 
-template <typename T, int R>
-__global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(GatedRecurrenceArgs a) {
+// COLUMNS: state columns of a block, one a lane of a group of COLUMNS lanes (32: a warp; 16: half a warp, for steps
+// that would otherwise leave most SMs with one block or none); GROUPS = 256 / COLUMNS groups share the state's rows.
+template <typename T, int R, int COLUMNS>
+__global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurrenceArgs a) {
     extern __shared__ __align__(16) float shared[];
-    constexpr int THREADS = GROUPS * COLUMNS;
+    constexpr int GROUPS = THREADS / COLUMNS;
     constexpr int PADDED = GROUPS * R;                   // dim rounded up: rows beyond dim hold q = 0, f = 1
     constexpr int GATES = (CHUNK * PADDED + THREADS - 1) / THREADS;     // (q, f) pairs a thread stages a chunk
     constexpr int VALUES = CHUNK * COLUMNS / THREADS;
@@ -74,9 +87,15 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
         const int d = g * R + j;
         S[j] = live && d < dim ? state[(long long)d * vdim + v] : 0.f;
     }
-    const float* bias = a.f_bias + head * dim;
-    const float* lower = a.lower + head * dim;
-    float raw_q[GATES], raw_f[GATES], raw_v[VALUES];
+    // the bias and the lower bound of the gates this thread stages: the same rows d in every chunk
+    float my_bias[GATES], my_lower[GATES];
+#pragma unroll
+    for (int i = 0; i < GATES; ++i) {
+        const int d = (threadIdx.x + i * THREADS) % PADDED;
+        my_bias[i] = d < dim ? a.f_bias[head * dim + d] : 0.f;
+        my_lower[i] = d < dim ? a.lower[head * dim + d] : 0.f;
+    }
+    typename Raw<T>::type raw_q[GATES], raw_f[GATES], raw_v[VALUES];
 
     // the raw projections of the chunk that starts at token t0, into registers (all loads in flight together)
     auto fetch = [&](int t0) {
@@ -84,20 +103,20 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
 #pragma unroll
         for (int i = 0; i < GATES; ++i) {
             const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
-            raw_q[i] = raw_f[i] = 0.f;
+            raw_q[i] = raw_f[i] = 0;
             if (t < tokens && d < dim) {
                 const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
-                raw_q[i] = load_here(row + head * dim + d);
-                raw_f[i] = load_here(row + (a.heads + head) * dim + d);
+                raw_q[i] = Raw<T>::load(row + head * dim + d);
+                raw_f[i] = Raw<T>::load(row + (a.heads + head) * dim + d);
             }
         }
 #pragma unroll
         for (int i = 0; i < VALUES; ++i) {
             const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
             const int column = blockIdx.z * COLUMNS + c;
-            raw_v[i] = 0.f;
+            raw_v[i] = 0;
             if (t < tokens && column < vdim)
-                raw_v[i] = load_here((const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld + 2 * a.heads * dim + head * vdim + column);
+                raw_v[i] = Raw<T>::load((const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld + 2 * a.heads * dim + head * vdim + column);
         }
     };
     // activations and gates of the fetched chunk, into a stage of shared memory
@@ -108,9 +127,10 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
             if (index >= CHUNK * PADDED) continue;
             float q = 0.f, f = 1.f;
             if (d < dim) {
-                q = raw_q[i] / (1.0f + expf(-raw_q[i]));
-                const float gate = 1.0f / (1.0f + expf(-(raw_f[i] + bias[d])));
-                f = lower[d] + (1.0f - lower[d]) * gate;
+                const float raw = Raw<T>::value(raw_q[i]);
+                q = raw / (1.0f + expf(-raw));
+                const float gate = 1.0f / (1.0f + expf(-(Raw<T>::value(raw_f[i]) + my_bias[i])));
+                f = my_lower[i] + (1.0f - my_lower[i]) * gate;
             }
             target[t * (2 * PADDED + COLUMNS) + d] = q;
             target[t * (2 * PADDED + COLUMNS) + PADDED + d] = f;
@@ -118,7 +138,7 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
 #pragma unroll
         for (int i = 0; i < VALUES; ++i) {
             const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
-            target[t * (2 * PADDED + COLUMNS) + 2 * PADDED + c] = raw_v[i];
+            target[t * (2 * PADDED + COLUMNS) + 2 * PADDED + c] = Raw<T>::value(raw_v[i]);
         }
     };
 
@@ -181,35 +201,46 @@ __global__ void __launch_bounds__(GROUPS * COLUMNS) gated_recurrence_kernel(Gate
     }
 }
 
-template <typename T, int R>
+template <typename T, int R, int COLUMNS>
 int launch(const GatedRecurrenceArgs& a, cudaStream_t stream) {
+    constexpr int GROUPS = THREADS / COLUMNS;
     const size_t shared = (size_t)2 * (CHUNK * (2 * GROUPS * R + COLUMNS) + CHUNK * GROUPS * COLUMNS) * sizeof(float);
-    auto kernel = gated_recurrence_kernel<T, R>;
+    auto kernel = gated_recurrence_kernel<T, R, COLUMNS>;
     if (shared > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
     dim3 grid(a.seqs, a.heads, (a.vdim + COLUMNS - 1) / COLUMNS);
-    return kidi_launch(kernel, grid, GROUPS * COLUMNS, shared, stream, a);
+    return kidi_launch(kernel, grid, THREADS, shared, stream, a);
+}
+
+template <typename T, int COLUMNS>
+int dispatch_rows(const GatedRecurrenceArgs& a, cudaStream_t stream) {
+    const int rows = (a.dim + THREADS / COLUMNS - 1) / (THREADS / COLUMNS);
+    if (rows <= 1) return launch<T, 1, COLUMNS>(a, stream);
+    if (rows <= 2) return launch<T, 2, COLUMNS>(a, stream);
+    if (rows <= 4) return launch<T, 4, COLUMNS>(a, stream);
+    if (rows <= 8) return launch<T, 8, COLUMNS>(a, stream);
+    if (rows <= 16) return launch<T, 16, COLUMNS>(a, stream);
+    if (COLUMNS == 32 && rows <= 32) return launch<T, 32, 32>(a, stream);
+    return KIDI_REFUSED_SIZE;
 }
 
 template <typename T>
 int dispatch(const GatedRecurrenceArgs& a, cudaStream_t stream) {
-    const int rows = (a.dim + GROUPS - 1) / GROUPS;
-    if (rows <= 1) return launch<T, 1>(a, stream);
-    if (rows <= 2) return launch<T, 2>(a, stream);
-    if (rows <= 4) return launch<T, 4>(a, stream);
-    if (rows <= 8) return launch<T, 8>(a, stream);
-    if (rows <= 16) return launch<T, 16>(a, stream);
-    if (rows <= 32) return launch<T, 32>(a, stream);
-    return KIDI_REFUSED_SIZE;
+    // Few (sequence, head, 32 columns) blocks: half as many columns a block, so that SMs hold two blocks or more.
+    // The choice depends on the step's sizes only through the number of sequences; a row's result does not
+    // depend on it beyond the order in which the partial read-outs are added.
+    const long long blocks = (long long)a.seqs * a.heads * ((a.vdim + 31) / 32);
+    if (a.narrow_blocks && blocks < 2 * 148 && a.vdim > 16) return dispatch_rows<T, 16>(a, stream);
+    return dispatch_rows<T, 32>(a, stream);
 }
 }  // namespace
 
 KIDI_API int kidi_gated_recurrence(const GatedRecurrenceArgs* args, int dtype, cudaStream_t stream) {
     const GatedRecurrenceArgs& a = *args;
     if (a.seqs <= 0) return 0;
-    if (a.heads <= 0 || a.heads > 65535 || a.dim <= 0 || a.vdim <= 0 || (a.vdim + COLUMNS - 1) / COLUMNS > 65535)
+    if (a.heads <= 0 || a.heads > 65535 || a.dim <= 0 || a.vdim <= 0 || (a.vdim + 15) / 16 > 65535)
         return KIDI_REFUSED_SIZE;
     if (dtype == KIDI_F32) return dispatch<float>(a, stream);
     if (dtype == KIDI_BF16) return dispatch<bf16>(a, stream);

@@ -16,7 +16,7 @@ class RecurrenceArgs(ctypes.Structure):
     _fields_ = [("qfv", c_void_p), ("ld", c_longlong), ("f_bias", c_void_p), ("lower", c_void_p),
                 ("state", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p),
                 ("seq_slot", c_void_p), ("seq_row0", c_void_p), ("seq_len", c_void_p), ("seqs", c_int),
-                ("heads", c_int), ("dim", c_int), ("vdim", c_int)]
+                ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("narrow_blocks", c_int)]
 
 
 _library = None
@@ -33,10 +33,12 @@ def library():
 
 
 def gated_recurrence(qfv: torch.Tensor, out: torch.Tensor, state: torch.Tensor, *, f_bias: torch.Tensor,
-                     lower: torch.Tensor, heads: int, dim: int, vdim: int, tables, seqs: int) -> None:
+                     lower: torch.Tensor, heads: int, dim: int, vdim: int, tables, seqs: int,
+                     many_tokens: bool = False) -> None:
     """Runs every sequence's rows of the step through the recurrence, from and into `state`
     [slots + 1, heads, dim, vdim] (float32). qfv [rows, 2*heads*dim + heads*vdim] holds the raw projections
-    [q | f | v]; out [rows, heads*vdim] gets each head's read-out S^T q, not yet normalised."""
+    [q | f | v]; out [rows, heads*vdim] gets each head's read-out S^T q, not yet normalised. `many_tokens`: the
+    step brings many tokens a sequence (a prompt), so few blocks would run for long: they are made narrower."""
     ops._need_cuda(qfv, out, state, f_bias, lower)
     rows = qfv.shape[0]
     if qfv.shape != (rows, 2 * heads * dim + heads * vdim) or out.shape != (rows, heads * vdim) or out.dtype != qfv.dtype \
@@ -52,5 +54,5 @@ def gated_recurrence(qfv: torch.Tensor, out: torch.Tensor, state: torch.Tensor, 
     args = RecurrenceArgs(qfv.data_ptr(), qfv.stride(0), f_bias.data_ptr(), lower.data_ptr(),
                           state.data_ptr(), out.data_ptr(), out.stride(0), tables.row_seq.data_ptr(),
                           tables.seq_slot.data_ptr(), tables.seq_row0.data_ptr(), tables.seq_len.data_ptr(), seqs,
-                          heads, dim, vdim)
+                          heads, dim, vdim, 1 if many_tokens else 0)
     _check(library().kidi_gated_recurrence(ctypes.byref(args), dtype_code(qfv.dtype), ops._stream()), "gated_recurrence")

@@ -80,5 +80,5 @@ class GatedRecurrence(Part):
         read = torch.empty((qfv.shape[0], self.heads * self.vdim), dtype=qfv.dtype, device=qfv.device)
         recurrence_kernels.gated_recurrence(qfv, read, views[0], f_bias=self.f_bias, lower=self.lower,
                                             heads=self.heads, dim=self.dim, vdim=self.vdim, tables=ctx.tables,
-                                            seqs=ctx.plan.n_seqs)
+                                            seqs=ctx.plan.n_seqs, many_tokens=ctx.plan.max_new >= 64)
         return self.out.forward(ops.rms_rows(read, self.vdim, self.norm, self.eps, out=read))
