@@ -111,6 +111,7 @@ poly_norm_bf16x8_kernel(const bf16* __restrict__ z, bf16* __restrict__ out, cons
     const uint4* source = reinterpret_cast<const uint4*>(z + row * width);
     const int pieces = width >> 3;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < pieces; i += ROW_THREADS) {
         const uint4 piece = source[i];
         const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&piece);
@@ -128,6 +129,7 @@ poly_norm_bf16x8_kernel(const bf16* __restrict__ z, bf16* __restrict__ out, cons
     const float r3 = 1.0f / sqrtf(block_sum<ROW_THREADS>(s6, scratch) / (float)width + eps);
     const float a = coefficients[0] * r1, b = coefficients[1] * r2, c3 = coefficients[2] * r3, e0 = coefficients[3];
     uint4* target = reinterpret_cast<uint4*>(out + row * width);
+#pragma unroll 4
     for (int i = threadIdx.x; i < pieces; i += ROW_THREADS) {
         uint4 piece = source[i];
         __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&piece);
