@@ -293,3 +293,23 @@ def test_which_kernels_run(record_property):
         run(engine32, slot, tokens)
     assert names.count("latent_attention") == 3 and "latent_pack" not in names and "library_mm" not in names
     assert not any("tcgen05" in name or "skinny" in name for name in names)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_heads_and_wide_states(dtype, record_property):
+    """Twenty heads (two tiles of sixteen for the tensor-core folded kernel, the second partly filled) over a cached
+    latent, and recurrent heads of 160 state rows (more than a warp's slice of 16 rows at 8 warps) by 40 columns
+    (no multiple of a block's 32 or 16)."""
+    config = sanozen_configs.model(80, 96, 2.0, 1e-5, 8, [
+        sanozen_configs.latent(20, 16, 16, 8, 24, 32, 0.3, 20000.0, 16, ff=128),
+        sanozen_configs.recurrent(2, 160, 40),
+        sanozen_configs.latent(20, 16, 16, 24, 24, 32, 0.3, 20000.0, 16, kv_from=0)])
+    tensors = sanozen_configs.tensors(config, 12)
+    engine, _, _ = make(None, dtype, config=config, tensors=tensors)
+    tokens = prompt(config, 140, 13)
+    want = plain(config, tensors, tokens)
+    slot = engine.acquire()
+    rows = [run(engine, slot, tokens[:70])] + [run(engine, slot, tokens[70:75])] + \
+           [run(engine, slot, [token]) for token in tokens[75:]]
+    engine.release(slot)
+    close(torch.cat(rows), want, dtype, record_property, "many heads")
