@@ -13,8 +13,11 @@
 // projections are loaded into registers before the current chunk's tokens are walked, so their latency hides
 // behind the walk); the eight partial read-outs of a column meet in shared memory and are added in the order of g. A token's result therefore depends on the sizes only: not on
 // what else is in the step, nor on how the sequence was cut into steps. The read-out leaves the kernel
-// unnormalised (its columns lie in different blocks); the norm over vdim is a kernel of its own.
+// unnormalised (its columns lie in different blocks); the norm over vdim is a kernel of its own. For steps of many
+// tokens q and f are computed once a row by a kernel of their own (into scratch memory), since every block of
+// columns of a head would otherwise compute them again.
 #include "common.cuh"
+#include <type_traits>
 
 struct GatedRecurrenceArgs {
     const void* qfv;       // [rows, ld]: heads*dim of q~, heads*dim of f~, heads*vdim of v
@@ -29,7 +32,10 @@ struct GatedRecurrenceArgs {
     const int* seq_row0;   // [seqs]
     const int* seq_len;    // [seqs]
     int seqs, heads, dim, vdim;
+    int rows;              // rows of the step (of qfv, out and gates)
     int narrow_blocks;     // the step brings many tokens a sequence: blocks of 16 columns when there are few blocks
+    float* gates;          // [rows, 2*heads*dim] or null: scratch for q and f computed once a row by a kernel of
+                           // their own (steps of many tokens), instead of once a block of columns inside the walk
 };
 
 namespace {
@@ -62,9 +68,26 @@ constexpr int CHUNK = 16;       // tokens whose gates are staged at a time
 
 // COLUMNS: state columns of a block, one a lane of a group of COLUMNS lanes (32: a warp; 16: half a warp, for steps
 // that would otherwise leave most SMs with one block or none); GROUPS = 256 / COLUMNS groups share the state's rows.
-template <typename T, int R, int COLUMNS>
+// q = silu(q~) and f = l + (1 - l) sigmoid(f~ + b) of every row, head and state row, once: [rows, 2*heads*dim].
+template <typename T>
+__global__ void recurrence_gates_kernel(GatedRecurrenceArgs a, long long total) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const int width = a.heads * a.dim;
+    const long long row = index / width;
+    const int c = (int)(index - row * width);
+    const T* source = (const T*)a.qfv + row * a.ld;
+    const float raw = to_float(source[c]);
+    const float gate = 1.0f / (1.0f + expf(-(to_float(source[width + c]) + a.f_bias[c])));
+    a.gates[row * 2 * width + c] = raw / (1.0f + expf(-raw));
+    a.gates[row * 2 * width + width + c] = a.lower[c] + (1.0f - a.lower[c]) * gate;
+}
+
+// PRE: q and f come computed from `a.gates`.
+template <typename T, int R, int COLUMNS, bool PRE>
 __global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurrenceArgs a) {
     extern __shared__ __align__(16) float shared[];
+    typedef typename std::conditional<PRE, float, T>::type G;    // what the staged q and f are loaded as
     constexpr int GROUPS = THREADS / COLUMNS;
     constexpr int PADDED = GROUPS * R;                   // dim rounded up: rows beyond dim hold q = 0, f = 1
     constexpr int GATES = (CHUNK * PADDED + THREADS - 1) / THREADS;     // (q, f) pairs a thread stages a chunk
@@ -95,7 +118,8 @@ __global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurren
         my_bias[i] = d < dim ? a.f_bias[head * dim + d] : 0.f;
         my_lower[i] = d < dim ? a.lower[head * dim + d] : 0.f;
     }
-    typename Raw<T>::type raw_q[GATES], raw_f[GATES], raw_v[VALUES];
+    typename Raw<G>::type raw_q[GATES], raw_f[GATES];
+    typename Raw<T>::type raw_v[VALUES];
 
     // the raw projections of the chunk that starts at token t0, into registers (all loads in flight together)
     auto fetch = [&](int t0) {
@@ -105,9 +129,15 @@ __global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurren
             const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
             raw_q[i] = raw_f[i] = 0;
             if (t < tokens && d < dim) {
-                const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
-                raw_q[i] = Raw<T>::load(row + head * dim + d);
-                raw_f[i] = Raw<T>::load(row + (a.heads + head) * dim + d);
+                if constexpr (PRE) {
+                    const float* row = a.gates + (long long)(row0 + t0 + t) * 2 * a.heads * dim;
+                    raw_q[i] = Raw<float>::load(row + head * dim + d);
+                    raw_f[i] = Raw<float>::load(row + (a.heads + head) * dim + d);
+                } else {
+                    const T* row = (const T*)a.qfv + (long long)(row0 + t0 + t) * a.ld;
+                    raw_q[i] = Raw<T>::load(row + head * dim + d);
+                    raw_f[i] = Raw<T>::load(row + (a.heads + head) * dim + d);
+                }
             }
         }
 #pragma unroll
@@ -127,10 +157,15 @@ __global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurren
             if (index >= CHUNK * PADDED) continue;
             float q = 0.f, f = 1.f;
             if (d < dim) {
-                const float raw = Raw<T>::value(raw_q[i]);
-                q = raw / (1.0f + expf(-raw));
-                const float gate = 1.0f / (1.0f + expf(-(Raw<T>::value(raw_f[i]) + my_bias[i])));
-                f = my_lower[i] + (1.0f - my_lower[i]) * gate;
+                if constexpr (PRE) {
+                    q = raw_q[i];
+                    f = raw_f[i];
+                } else {
+                    const float raw = Raw<T>::value(raw_q[i]);
+                    q = raw / (1.0f + expf(-raw));
+                    const float gate = 1.0f / (1.0f + expf(-(Raw<T>::value(raw_f[i]) + my_bias[i])));
+                    f = my_lower[i] + (1.0f - my_lower[i]) * gate;
+                }
             }
             target[t * (2 * PADDED + COLUMNS) + d] = q;
             target[t * (2 * PADDED + COLUMNS) + PADDED + d] = f;
@@ -201,17 +236,25 @@ __global__ void __launch_bounds__(THREADS) gated_recurrence_kernel(GatedRecurren
     }
 }
 
-template <typename T, int R, int COLUMNS>
-int launch(const GatedRecurrenceArgs& a, cudaStream_t stream) {
+template <typename T, int R, int COLUMNS, bool PRE>
+int launch_form(const GatedRecurrenceArgs& a, cudaStream_t stream) {
     constexpr int GROUPS = THREADS / COLUMNS;
     const size_t shared = (size_t)2 * (CHUNK * (2 * GROUPS * R + COLUMNS) + CHUNK * GROUPS * COLUMNS) * sizeof(float);
-    auto kernel = gated_recurrence_kernel<T, R, COLUMNS>;
+    auto kernel = gated_recurrence_kernel<T, R, COLUMNS, PRE>;
     if (shared > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (status != cudaSuccess) return (int)status;
     }
     dim3 grid(a.seqs, a.heads, (a.vdim + COLUMNS - 1) / COLUMNS);
     return kidi_launch(kernel, grid, THREADS, shared, stream, a);
+}
+
+template <typename T, int R, int COLUMNS>
+int launch(const GatedRecurrenceArgs& a, cudaStream_t stream) {
+    if (!a.gates) return launch_form<T, R, COLUMNS, false>(a, stream);
+    const long long total = (long long)a.rows * a.heads * a.dim;
+    const int status = kidi_launch(recurrence_gates_kernel<T>, (unsigned)((total + 255) / 256), 256, 0, stream, a, total);
+    return status ? status : launch_form<T, R, COLUMNS, true>(a, stream);
 }
 
 template <typename T, int COLUMNS>

@@ -16,7 +16,8 @@ class RecurrenceArgs(ctypes.Structure):
     _fields_ = [("qfv", c_void_p), ("ld", c_longlong), ("f_bias", c_void_p), ("lower", c_void_p),
                 ("state", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p),
                 ("seq_slot", c_void_p), ("seq_row0", c_void_p), ("seq_len", c_void_p), ("seqs", c_int),
-                ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("narrow_blocks", c_int)]
+                ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("rows", c_int), ("narrow_blocks", c_int),
+                ("gates", c_void_p)]
 
 
 _library = None
@@ -51,8 +52,11 @@ def gated_recurrence(qfv: torch.Tensor, out: torch.Tensor, state: torch.Tensor, 
     for vector, size in ((f_bias, heads * dim), (lower, heads * dim)):
         if vector.dtype != torch.float32 or vector.shape != (size,) or not vector.is_contiguous():
             raise invalid_argument("gated recurrence: bias and lower bound are float32 vectors")
+    # many tokens a sequence: the gates of a row are computed once, by a kernel of their own, into scratch memory
+    gates = torch.empty((rows, 2 * heads * dim), dtype=torch.float32, device=qfv.device) if many_tokens else None
     args = RecurrenceArgs(qfv.data_ptr(), qfv.stride(0), f_bias.data_ptr(), lower.data_ptr(),
                           state.data_ptr(), out.data_ptr(), out.stride(0), tables.row_seq.data_ptr(),
                           tables.seq_slot.data_ptr(), tables.seq_row0.data_ptr(), tables.seq_len.data_ptr(), seqs,
-                          heads, dim, vdim, 1 if many_tokens else 0)
-    _check(library().kidi_gated_recurrence(ctypes.byref(args), dtype_code(qfv.dtype), ops._stream()), "gated_recurrence")
+                          heads, dim, vdim, rows, 1 if many_tokens else 0, gates.data_ptr() if gates is not None else 0)
+    _check(library().kidi_gated_recurrence(ctypes.byref(args), dtype_code(qfv.dtype), ops._stream()),
+           "gated_recurrence[gates apart]" if gates is not None else "gated_recurrence", 2 if gates is not None else 1)

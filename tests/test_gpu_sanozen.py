@@ -272,7 +272,7 @@ def test_which_kernels_run(record_property):
     engine.release(slot)
     assert names.count("latent_pack") == 3 and names.count("latent_gather") == 1 and "latent_attention" not in names
     assert names.count("attention_prefill_tcgen05") == 2 and names.count("attention_prefill[mma.sync]") == 1
-    assert names.count("gated_recurrence") == 2 and names.count("add_layernorm") == 5 + 3 + 1
+    assert names.count("gated_recurrence[gates apart]") == 2 and names.count("add_layernorm") == 5 + 3 + 1
     slot = engine.acquire()
     run(engine, slot, tokens[:1], want=[])
     with ops.record_launches() as names:
