@@ -44,6 +44,8 @@ LIBRARIES: Dict[str, Tuple[str, ...]] = {
     # mixers that only some architectures have: built when a model with such a layer first runs
     "latent_attention": ("latent_attention.cu",),
     "gated_recurrence": ("gated_recurrence.cu",),
+    "differential_attention": ("differential_attention.cu",),
+    "routed": ("routed.cu",),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,246 @@
+// A feed-forward made of many small gated experts, of which each token uses a few.
+//
+//   z = W_router h (32-bit), s = score(z); the `top` experts with the largest scores are taken
+//   (ties: the lower index) with weights w = s (optionally divided by their sum);
+//   y = sum over the chosen experts of  scale_out * W_down[e] (act(W_gate[e] x) * (W_up[e] x)),
+//   x = scale_in * h, where the weight w is scale_in (a weight on the expert's input) or scale_out
+//   (on its output) and the other is 1. act is SiLU.
+//
+// A (row, choice) pair is a "slot": slot = row * top + choice.
+//
+// Kernels:
+//  * choose: scores, the top choices and their weights, a warp a row;
+//  * slots, gate and up: for few rows, and for every row count of the 32-bit engine: a warp per
+//    (slot, feature) reads the chosen expert's two weight rows once and applies the activation; the
+//    input weight is applied to the two products in 32-bit (W (w h) = w (W h));
+//  * slots, down: a warp per (row, feature) sums its choices' products in the order of the choices;
+//  * gather / combine: for many rows the slots are sorted by expert on the host, their scaled input
+//    rows gathered, each expert's rows run through the ordinary products, and the results summed per
+//    row in the order of the choices.
+// Nothing here depends on which other rows share the step: a row's result is the same alone and in
+// a batch.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- choose
+// logits [rows, experts] float; a warp a row; scores staged in shared memory (experts <= 1024).
+__global__ void __launch_bounds__(128) route_choose_kernel(const float* __restrict__ logits, int* __restrict__ chosen,
+                                                           float* __restrict__ weight, int rows, int experts, int top,
+                                                           int renormalise) {
+    extern __shared__ float staged[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    float* score = staged + (long long)warp * experts;
+    for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-logits[(long long)row * experts + e]));
+    __syncwarp();
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float s = score[e];
+            if (s > best) { best = s; at = e; }          // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+            if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+        }
+        if (at == 0x7fffffff) at = 0;                     // every score a NaN
+        if (lane == 0) {
+            chosen[(long long)row * top + k] = at;
+            weight[(long long)row * top + k] = best;
+            score[at] = -INFINITY;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renormalise && lane < top) weight[(long long)row * top + lane] /= total;
+}
+
+KIDI_API int kidi_route_choose(const float* logits, int* chosen, float* weight, int rows, int experts, int top,
+                               int renormalise, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32) return KIDI_REFUSED_SIZE;
+    return kidi_launch(route_choose_kernel, (unsigned)((rows + 3) / 4), 128, (size_t)4 * experts * sizeof(float), stream,
+                       logits, chosen, weight, rows, experts, top, renormalise);
+}
+
+// ------------------------------------------------------------------ dots
+// Two rows of weights against one row of x, a warp's share; the caller sums over the warp.
+template <typename T>
+__device__ __forceinline__ void dot2(const T* __restrict__ wa, const T* __restrict__ wb, const T* __restrict__ x, int K,
+                                     int lane, float& a, float& b) {
+    for (int k = lane; k < K; k += 32) {
+        const float v = to_float(x[k]);
+        a = fmaf(to_float(wa[k]), v, a);
+        b = fmaf(to_float(wb[k]), v, b);
+    }
+}
+template <>
+__device__ __forceinline__ void dot2<bf16>(const bf16* __restrict__ wa, const bf16* __restrict__ wb,
+                                           const bf16* __restrict__ x, int K, int lane, float& a, float& b) {
+    if ((K & 7) || ((uintptr_t)wa & 15) || ((uintptr_t)wb & 15) || ((uintptr_t)x & 15)) {
+        for (int k = lane; k < K; k += 32) {
+            const float v = to_float(x[k]);
+            a = fmaf(to_float(wa[k]), v, a);
+            b = fmaf(to_float(wb[k]), v, b);
+        }
+        return;
+    }
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 ra = *reinterpret_cast<const uint4*>(wa + k), rb = *reinterpret_cast<const uint4*>(wb + k);
+        const uint4 rx = *reinterpret_cast<const uint4*>(x + k);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+        const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&rx);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]), fx = __bfloat1622float2(px[i]);
+            a = fmaf(fa.x, fx.x, a); a = fmaf(fa.y, fx.y, a);
+            b = fmaf(fb.x, fx.x, b); b = fmaf(fb.y, fx.y, b);
+        }
+    }
+}
+
+// ----------------------------------------------------- slots: gate and up
+// gate_up [experts, 2 * inter, hidden] (gate rows, then up rows); mid [rows * top, inter].
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) expert_gate_up_kernel(const T* __restrict__ x, const TW* __restrict__ gate_up,
+                                                             const int* __restrict__ chosen, const float* __restrict__ weight,
+                                                             T* __restrict__ mid, long long slots, int top, int hidden,
+                                                             int inter, int weight_on_input) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= slots * inter) return;
+    const long long slot = item / inter;
+    const int n = (int)(item - slot * inter);
+    const int expert = chosen[slot];
+    const TW* base = gate_up + (long long)expert * 2 * inter * hidden;
+    const T* row = x + (slot / top) * hidden;
+    float g = 0.f, u = 0.f;
+    if constexpr (sizeof(T) == sizeof(TW)) dot2<T>((const T*)base + (long long)n * hidden,
+                                                   (const T*)base + (long long)(inter + n) * hidden, row, hidden, lane, g, u);
+    else
+        for (int k = lane; k < hidden; k += 32) {
+            const float v = to_float(row[k]);
+            g = fmaf(to_float(base[(long long)n * hidden + k]), v, g);
+            u = fmaf(to_float(base[(long long)(inter + n) * hidden + k]), v, u);
+        }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+        const float w = weight_on_input ? weight[slot] : 1.f;
+        g *= w;
+        u *= w;
+        mid[slot * inter + n] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------- slots: down
+// down [experts, hidden, inter]; out [rows, hidden] = sum over a row's choices, in their order.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) expert_down_kernel(const T* __restrict__ mid, const TW* __restrict__ down,
+                                                          const int* __restrict__ chosen, const float* __restrict__ weight,
+                                                          T* __restrict__ out, long long rows, int top, int hidden, int inter,
+                                                          int weight_on_input) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= rows * hidden) return;
+    const long long row = item / hidden;
+    const int n = (int)(item - row * hidden);
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const long long slot = row * top + k;
+        const TW* w = down + ((long long)chosen[slot] * hidden + n) * inter;
+        const T* m = mid + slot * inter;
+        float a = 0.f, unused = 0.f;
+        if constexpr (sizeof(T) == sizeof(TW)) dot2<T>((const T*)w, (const T*)w, m, inter, lane, a, unused);
+        else
+            for (int i = lane; i < inter; i += 32) a = fmaf(to_float(w[i]), to_float(m[i]), a);
+        a = warp_sum(a);
+        total += weight_on_input ? a : a * weight[slot];
+    }
+    if (lane == 0) out[row * hidden + n] = from_float<T>(total);
+}
+
+KIDI_API int kidi_expert_slots(const void* x, int dtype, const void* gate_up, const void* down, int weight_dtype,
+                               const int* chosen, const float* weight, void* mid, void* out, int rows, int top,
+                               int hidden, int inter, int weight_on_input, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const long long slots = (long long)rows * top;
+    const long long first = slots * inter, second = (long long)rows * hidden;
+    if (first >= (1LL << 33) || second >= (1LL << 33)) return KIDI_REFUSED_SIZE;
+#define KIDI_CASE(D, T, W, TW)                                                                                     \
+    if (dtype == D && weight_dtype == W) {                                                                         \
+        int status = kidi_launch(expert_gate_up_kernel<T, TW>, (unsigned)((first + 3) / 4), 128, 0, stream,       \
+                                 (const T*)x, (const TW*)gate_up, chosen, weight, (T*)mid, slots, top, hidden,     \
+                                 inter, weight_on_input);                                                          \
+        if (status) return status;                                                                                 \
+        return kidi_launch(expert_down_kernel<T, TW>, (unsigned)((second + 3) / 4), 128, 0, stream, (const T*)mid, \
+                           (const TW*)down, chosen, weight, (T*)out, (long long)rows, top, hidden, inter,          \
+                           weight_on_input);                                                                       \
+    }
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+// ------------------------------------------------------ gather / combine
+// gathered[i] = x[order[i] / top] * (weight[order[i]] or 1): the slots' input rows in the order of their experts.
+template <typename T>
+__global__ void gather_slots_kernel(const T* __restrict__ x, const int* __restrict__ order, const float* __restrict__ weight,
+                                    T* __restrict__ gathered, long long total, int top, int hidden, int weight_on_input) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long i = index / hidden;
+    const int c = (int)(index - i * hidden);
+    const int slot = order[i];
+    const float w = weight_on_input ? weight[slot] : 1.f;
+    gathered[index] = from_float<T>(to_float(x[(long long)(slot / top) * hidden + c]) * w);
+}
+
+// out[row] = sum over the row's choices k of y[place[row * top + k]] (* weight), in the order of the choices.
+template <typename T>
+__global__ void combine_slots_kernel(const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weight,
+                                     T* __restrict__ out, long long total, int top, int hidden, int weight_on_input) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / hidden;
+    const int c = (int)(index - row * hidden);
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const long long slot = row * top + k;
+        const float value = to_float(y[(long long)place[slot] * hidden + c]);
+        sum += weight_on_input ? value : value * weight[slot];
+    }
+    out[index] = from_float<T>(sum);
+}
+
+KIDI_API int kidi_gather_slots(const void* x, int dtype, const int* order, const float* weight, void* gathered, int slots,
+                               int top, int hidden, int weight_on_input, cudaStream_t stream) {
+    const long long total = (long long)slots * hidden;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(gather_slots_kernel<float>, blocks, 256, 0, stream, (const float*)x, order,
+                                              weight, (float*)gathered, total, top, hidden, weight_on_input);
+    if (dtype == KIDI_BF16) return kidi_launch(gather_slots_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)x, order,
+                                               weight, (bf16*)gathered, total, top, hidden, weight_on_input);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_combine_slots(const void* y, int dtype, const int* place, const float* weight, void* out, int rows,
+                                int top, int hidden, int weight_on_input, cudaStream_t stream) {
+    const long long total = (long long)rows * hidden;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(combine_slots_kernel<float>, blocks, 256, 0, stream, (const float*)y, place,
+                                              weight, (float*)out, total, top, hidden, weight_on_input);
+    if (dtype == KIDI_BF16) return kidi_launch(combine_slots_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)y, place,
+                                               weight, (bf16*)out, total, top, hidden, weight_on_input);
+    return KIDI_REFUSED_DTYPE;
+}

@@ -317,3 +317,73 @@ KIDI_API int kidi_add_cast(float* x, const void* delta, int delta_dtype, void* c
 #undef KIDI_CASE
     return KIDI_REFUSED_DTYPE;
 }
+
+// ---------------------------------------------------------------- rows of a table added to the stream
+// x[r, :] += table[index[r], :] * scale (x 32-bit, in place): a learned vector per position, say.
+// Rows whose index lies outside the table are left as they are.
+template <typename TW>
+__global__ void add_table_rows_kernel(float* __restrict__ x, const TW* __restrict__ table, const int* __restrict__ index,
+                                      long long total, int hidden, int table_rows, float scale) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at >= total) return;
+    const long long row = at / hidden;
+    const int c = (int)(at - row * hidden);
+    const int source = index[row];
+    if (source < 0 || source >= table_rows) return;
+    x[at] += to_float(table[(long long)source * hidden + c]) * scale;
+}
+
+KIDI_API int kidi_add_table_rows(float* x, const void* table, int table_dtype, const int* index, int rows, int hidden,
+                                 int table_rows, float scale, cudaStream_t stream) {
+    const long long total = (long long)rows * hidden;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (table_dtype == KIDI_F32)
+        return kidi_launch(add_table_rows_kernel<float>, blocks, 256, 0, stream, x, (const float*)table, index, total,
+                           hidden, table_rows, scale);
+    if (table_dtype == KIDI_BF16)
+        return kidi_launch(add_table_rows_kernel<bf16>, blocks, 256, 0, stream, x, (const bf16*)table, index, total,
+                           hidden, table_rows, scale);
+    return KIDI_REFUSED_DTYPE;
+}
+
+// ---------------------------------------------------------------- a bounded gate
+// gate_up [rows, 2 * inter] (gate columns, then up columns):
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + up_shift)
+template <typename T>
+__global__ void bounded_gate_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter,
+                                    float limit, float alpha, float up_shift) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / inter;
+    const int c = (int)(index - row * inter);
+    const float gate = fminf(to_float(gate_up[row * 2 * inter + c]), limit);
+    const float up = fminf(fmaxf(to_float(gate_up[row * 2 * inter + inter + c]), -limit), limit);
+    out[index] = from_float<T>(gate / (1.0f + expf(-alpha * gate)) * (up + up_shift));
+}
+
+KIDI_API int kidi_bounded_gate(const void* gate_up, void* out, int dtype, int rows, int inter, float limit, float alpha,
+                               float up_shift, cudaStream_t stream) {
+    const long long total = (long long)rows * inter;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32)
+        return kidi_launch(bounded_gate_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, total,
+                           inter, limit, alpha, up_shift);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(bounded_gate_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, total,
+                           inter, limit, alpha, up_shift);
+    return KIDI_REFUSED_DTYPE;
+}
+
+// ---------------------------------------------------------------- bounded logits
+// x <- cap * tanh(x / cap), 32-bit, in place.
+__global__ void tanh_cap_kernel(float* __restrict__ x, long long total, float cap) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index < total) x[index] = cap * tanhf(x[index] / cap);
+}
+
+KIDI_API int kidi_tanh_cap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    return kidi_launch(tanh_cap_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, total, cap);
+}

@@ -28,6 +28,8 @@ from ..parts import gated_recurrence as _gated_recurrence  # noqa: F401
 from ..parts import latent_attention as _latent_attention  # noqa: F401
 from ..parts import stream_mix as _stream_mix  # noqa: F401
 from ..parts import token_input as _token_input  # noqa: F401
+from ..parts import differential_attention as _differential_attention  # noqa: F401
+from ..parts import routed as _routed  # noqa: F401
 
 
 class CausalLM:
@@ -56,6 +58,8 @@ class CausalLM:
             if unknown:
                 raise invalid_argument(f"arrangement '{layer.arrangement.kind}' has no part '{unknown[0]}'")
             self.layers.append(arrangement(layer.arrangement, self.env, parts))
+        self.embedding_norm = part_registry.build_part("norm", spec.embedding_norm, self.env) \
+            if spec.embedding_norm is not None else None
         self.final_norm = part_registry.build_part("norm", spec.final_norm, self.env)
         self.head = part_registry.build_part("head", spec.head, self.env)
         self.schedule = list(spec.schedule)
@@ -68,7 +72,8 @@ class CausalLM:
 
     # ------------------------------------------------------------------ tensors
     def _top_parts(self) -> Sequence[Part]:
-        return [self.embedding, *self.env.positions.values(), *self.env.shared.values(), *self.layers,
+        return [self.embedding, *self.env.positions.values(), *self.env.shared.values(),
+                *([self.embedding_norm] if self.embedding_norm is not None else []), *self.layers,
                 self.final_norm, self.head]
 
     def parameters(self) -> List[Tuple[str, ParamSpec]]:
@@ -122,6 +127,8 @@ class CausalLM:
         stream = ResidualStream(self.embedding.forward(ctx.tables.tokens, ctx))
         for position in self.env.positions.values():
             position.on_embeddings(stream, ctx)
+        if self.embedding_norm is not None:
+            stream = ResidualStream(self.embedding_norm.forward(stream, out_dtype=torch.float32))
         for index, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]
             options = {}

@@ -173,6 +173,11 @@ def core():
                                                c_longlong, c_longlong, c_int, c_longlong, c_longlong, c_longlong,
                                                c_void_p]
         lib.kidi_gemm_rows_batched.restype = c_int
+        lib.kidi_add_table_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+        lib.kidi_bounded_gate.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p]
+        lib.kidi_tanh_cap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
+        for name in ("kidi_add_table_rows", "kidi_bounded_gate", "kidi_tanh_cap"):
+            getattr(lib, name).restype = c_int
         for name in ("kidi_add_layernorm", "kidi_rms_rows", "kidi_poly_norm", "kidi_token_gate", "kidi_add_normed_mix",
                      "kidi_add_cast", "kidi_gemm_simt_batched"):
             getattr(lib, name).restype = c_int
@@ -407,6 +412,41 @@ def silu_gate(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torc
     _check(core().kidi_silu_gate(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), rows, inter, _stream()),
            "silu_gate")
     return out
+
+
+def bounded_gate(gate_up: torch.Tensor, limit: float, alpha: float, up_shift: float) -> torch.Tensor:
+    """g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + up_shift) for
+    gate_up [rows, 2*I] (gate columns first)."""
+    _need_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise invalid_argument("bounded_gate takes a contiguous [rows, 2*I] matrix")
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(core().kidi_bounded_gate(_ptr(gate_up), _ptr(out), dtype_code(gate_up.dtype), rows, inter, float(limit),
+                                    float(alpha), float(up_shift), _stream()), "bounded_gate")
+    return out
+
+
+def add_table_rows(x: torch.Tensor, table: torch.Tensor, index: torch.Tensor, scale: float = 1.0) -> None:
+    """x[r] += table[index[r]] * scale (x float32, in place); rows whose index lies outside the table stay."""
+    _need_cuda(x, table, index)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise invalid_argument("the residual stream is a contiguous float32 matrix")
+    if table.dim() != 2 or table.shape[1] != x.shape[1] or not table.is_contiguous():
+        raise invalid_argument("add_table_rows: the table's rows must be as wide as the stream's")
+    if index.dtype != torch.int32 or index.dim() != 1 or index.shape[0] < x.shape[0]:
+        raise invalid_argument("add_table_rows takes an int32 index per row")
+    _check(core().kidi_add_table_rows(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(index), x.shape[0], x.shape[1],
+                                      table.shape[0], float(scale), _stream()), "add_table_rows")
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), float32, in place."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not cap > 0:
+        raise invalid_argument("tanh_cap takes a contiguous float32 tensor and a positive bound")
+    _check(core().kidi_tanh_cap(_ptr(x), x.numel(), float(cap), _stream()), "tanh_cap")
+    return x
 
 
 def check_bias(bias: Optional[torch.Tensor], features: int) -> None:

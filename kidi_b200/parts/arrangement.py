@@ -95,3 +95,36 @@ class PreNormBlock(Part):
             self.token_input.forward(stream, ctx, mix=self.stream_mix)
         elif self.stream_mix is not None:
             self.stream_mix.forward(stream, ctx)
+
+
+@register_part("arrangement", "parallel")
+class ParallelBlock(Part):
+    """One norm, and both sublayers read its output: h = norm(x), x <- x + (mixer(h) + feed_forward(h)).
+    The feed-forward is optional. Both results are added to the 32-bit stream: the feed-forward's at once,
+    the mixer's as the pending delta that the next norm adds while it normalises."""
+
+    ROLES = {"input_norm": "norm", "mixer": "mixer"}
+    OPTIONAL_ROLES = {"feed_forward": "feed_forward"}
+
+    def __init__(self, spec, env, parts: Dict[str, Part]):
+        super().__init__(spec, env)
+        self.input_norm = parts["input_norm"]
+        self.mixer = parts["mixer"]
+        self.feed_forward = parts.get("feed_forward")
+
+    def children(self):
+        return tuple(part for part in (self.input_norm, self.mixer, self.feed_forward) if part is not None)
+
+    def cache_requests(self) -> list:
+        return self.mixer.cache_requests()
+
+    def first_norm(self) -> Part:
+        return self.input_norm
+
+    def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool) -> None:
+        from ..kernels import ops
+        normed = plain_rows(self.input_norm.forward(stream))
+        mixed = self.mixer.forward(normed, ctx, views, owns_cache)
+        if self.feed_forward is not None:
+            ops.add_cast(stream.hidden, self.feed_forward.forward(normed, ctx), None)
+        stream.add(mixed)

@@ -5,7 +5,8 @@ Embedding: a row gather times a scalar scale into the 32-bit residual stream
 Head: logits = x W^T in 32-bit at the rows that were asked for; W may be the embedding
 table itself (tied). The reference's Qwen3 has no head; the generic causal path's
 "final norm -> lm_head -> 32-bit logits, selected rows only" is the precedent
-(src/kidi/model/gemma4.cpp:769-778,1057).
+(src/kidi/model/gemma4.cpp:769-778,1057). With the head's parameter `softcap` (default none) the
+logits are bounded: cap * tanh(logits / cap), in 32-bit.
 """
 from __future__ import annotations
 
@@ -48,6 +49,7 @@ class LinearHead(Part):
         self.hidden = int(spec.param("hidden_size"))
         self.tied_to = spec.param("tied_to", None)
         self.name = spec.param("name", "weight")
+        self.softcap = float(spec.param("softcap", 0.0) or 0.0)
         self.linear: Optional[Linear] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
@@ -57,4 +59,5 @@ class LinearHead(Part):
         self.linear = Linear(tensors[self.name])
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return self.linear.forward(x, out_dtype=torch.float32)
+        logits = self.linear.forward(x, out_dtype=torch.float32)
+        return ops.tanh_cap(logits, self.softcap) if self.softcap > 0 else logits

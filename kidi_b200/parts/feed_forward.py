@@ -5,7 +5,12 @@ projection to [gate | up] (gate = first I columns), the activation on the gate t
 up, then the down projection; no biases. SiLU is g / (1 + exp(-g))
 (src/kidi/runtime/mps/eager_kernels.metal:129-137).
 
-Parameters: hidden_size, intermediate_size, activation ("silu").
+Parameters: hidden_size, intermediate_size, activation, gate_name, up_name, down_name (tensor names under the
+prefix; default gate_proj.weight, up_proj.weight, down_proj.weight). Activations:
+
+* "silu": y = silu(g) * u;
+* "bounded_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift),
+  with the parameters limit, alpha (default 1.702) and up_shift (default 1).
 """
 from __future__ import annotations
 
@@ -13,7 +18,7 @@ from typing import List, Optional
 
 import torch
 
-from ..errors import unsupported
+from ..errors import invalid_argument, unsupported
 from ..kernels import ops
 from .base import Part, RowScaled
 from .linear import Linear
@@ -30,26 +35,39 @@ class GatedFeedForward(Part):
         super().__init__(spec, env)
         self.hidden = int(spec.param("hidden_size"))
         self.inter = int(spec.param("intermediate_size"))
-        activation = spec.param("activation", "silu")
-        if activation != "silu":
-            raise unsupported(f"gated feed-forward activation '{activation}' is not built (silu is)")
+        self.activation = spec.param("activation", "silu")
+        if self.activation not in ("silu", "bounded_swish"):
+            raise unsupported(f"gated feed-forward activation '{self.activation}' is not built "
+                              f"(silu and bounded_swish are)")
+        if self.activation == "bounded_swish":
+            self.limit = float(spec.param("limit"))
+            self.alpha = float(spec.param("alpha", 1.702))
+            self.up_shift = float(spec.param("up_shift", 1.0))
+            if not self.limit > 0:
+                raise invalid_argument("the bound of a bounded gate must be positive")
+        self.gate_name = spec.param("gate_name", "gate_proj.weight")
+        self.up_name = spec.param("up_name", "up_proj.weight")
+        self.down_name = spec.param("down_name", "down_proj.weight")
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
         return [
             ParamSpec("gate_up_proj.weight", (2 * self.inter, self.hidden), sources=(
-                ("gate_proj.weight", (self.inter, self.hidden)),
-                ("up_proj.weight", (self.inter, self.hidden)))),
-            ParamSpec("down_proj.weight", (self.hidden, self.inter)),
+                (self.gate_name, (self.inter, self.hidden)),
+                (self.up_name, (self.inter, self.hidden)))),
+            ParamSpec(self.down_name, (self.hidden, self.inter)),
         ]
 
     def bind(self, tensors) -> None:
         self.gate_up = Linear(tensors["gate_up_proj.weight"])
-        self.down = Linear(tensors["down_proj.weight"])
+        self.down = Linear(tensors[self.down_name])
 
     def forward(self, x, ctx, sink=None) -> Optional[torch.Tensor]:
         from ..kernels import skinny, tcgen05
+        if self.activation == "bounded_swish":
+            both = self.gate_up.forward(x)
+            return self.down.forward(ops.bounded_gate(both, self.limit, self.alpha, self.up_shift), sink=sink)
         factors = None
         if isinstance(x, RowScaled):
             if skinny.supports(x.values, self.gate_up.weight) and x.values.shape[0] <= skinny.MAX_ROWS:

@@ -4,6 +4,10 @@ The reference's RmsNorm (src/kidi/layers/gemma4.cpp:23-67; op contract
 src/kidi/ops/context.cpp:1043-1082; arithmetic
 src/kidi/runtime/mps/eager_kernels.metal:65-87). The norm is also where the residual
 stream takes its pending delta: sum and normalisation run in one kernel, in 32-bit.
+
+Parameters of `rms_norm`: size, eps, weight_name (the tensor's name under the prefix, default "weight") and
+weight_offset (default 0): the stored tensor plus this number is the weight, so a weight that a model stores
+around zero has weight_offset 1: y = x / sqrt(mean(x^2) + eps) * (1 + w).
 """
 from __future__ import annotations
 
@@ -23,22 +27,28 @@ class RMSNorm(Part):
         super().__init__(spec, env)
         self.size = int(spec.param("size"))
         self.eps = float(spec.param("eps"))
+        self.weight_name = spec.param("weight_name", "weight")
+        self.offset = float(spec.param("weight_offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.size,), init=("one_plus_normal", 0.1))]
+        init = ("normal", 0.1) if self.offset else ("one_plus_normal", 0.1)
+        return [ParamSpec(self.weight_name, (self.size,), init=init)]
 
     def bind(self, tensors) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+        if self.offset:           # the sum is formed once, in 32-bit
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def prepared_weight(self) -> Optional[torch.Tensor]:
         """The weight vector a product needs to prepare rows for this norm (`ResidualSink`), or
         None when this norm does not take prepared rows."""
-        return self.weight if self.env.dtype == torch.bfloat16 else None
+        return self.weight if self.env.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 else None
 
-    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False):
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False,
+                out_dtype: Optional[torch.dtype] = None):
         """Adds the stream's pending delta and returns the normalised rows in the
-        engine dtype. With `rows` (int32 indices) only those rows are produced and the
+        engine dtype (or `out_dtype`). With `rows` (int32 indices) only those rows are produced and the
         stream itself is left untouched. With `scaled` the caller takes a `RowScaled` too:
         when the product before has prepared the rows (added its result to the stream, multiplied
         by this norm's weight, summed the squares) there is nothing left to launch."""
@@ -46,8 +56,8 @@ class RMSNorm(Part):
         if prepared is not None:
             ready = RowScaled(prepared[0], prepared[1], self.size, self.eps)
             return ready if scaled else ready.plain()
-        return ops.add_rmsnorm(stream.hidden, stream.take_pending(), self.weight, self.eps, self.env.dtype,
-                               row_index=rows)
+        return ops.add_rmsnorm(stream.hidden, stream.take_pending(), self.weight, self.eps,
+                               out_dtype or self.env.dtype, row_index=rows)
 
 
 @register_part("norm", "layer_norm")

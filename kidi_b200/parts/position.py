@@ -5,6 +5,10 @@ angle = float(position) * freq_i, cos and sin of it, all in 32-bit, positions fr
 0 (src/kidi/model/qwen3.cpp:138-157). A mixer that rotates its queries and keys looks
 the encoding up by name in `env.positions` and hands `cos`/`sin` to its kernel.
 
+`learned_positions` is a table with a vector per position that is added to the embeddings
+(times `scale`, default 1), in 32-bit; mixers read nothing from it. Parameters: hidden_size,
+max_positions, scale, name (the table's tensor name under the prefix, default "weight").
+
 Interface of a position encoding: `on_embeddings(stream, ctx)` (may change the
 embeddings; rotary does nothing there) and whatever its mixers agree to read from it
 (`cos`, `sin`, `rotary_dim` here).
@@ -14,8 +18,10 @@ from __future__ import annotations
 import torch
 
 from ..errors import invalid_argument
+from ..kernels import ops
 from .base import Part
 from .registry import register_part
+from .spec import ParamSpec
 
 
 @register_part("position", "rotary")
@@ -57,3 +63,25 @@ class RotaryEncoding(Part):
 
     def on_embeddings(self, stream, ctx) -> None:
         return None
+
+
+@register_part("position", "learned_positions")
+class LearnedPositions(Part):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.max_positions = int(spec.param("max_positions"))
+        self.scale = float(spec.param("scale", 1.0))
+        self.name = spec.param("name", "weight")
+        if self.hidden <= 0 or self.max_positions <= 0:
+            raise invalid_argument("a position table needs a positive width and length")
+        self.table = None
+
+    def parameter_specs(self):
+        return [ParamSpec(self.name, (self.max_positions, self.hidden), init=("normal", 0.05))]
+
+    def bind(self, tensors) -> None:
+        self.table = tensors[self.name]
+
+    def on_embeddings(self, stream, ctx) -> None:
+        ops.add_table_rows(stream.hidden, self.table, ctx.tables.row_pos, self.scale)

@@ -67,6 +67,8 @@ class ModelSpec:
     shared: Mapping[str, PartSpec] = dataclasses.field(default_factory=dict)  # named parts (role "shared") built once
                                                                                # that several layers read
     ignored_tensors: Tuple[str, ...] = ()  # regular expressions of tensor names a file may carry unused
+    embedding_norm: Optional[PartSpec] = None  # a norm that the embeddings (with what the position encodings
+                                               # added) pass before the first layer; its result is the stream
 
 
 @dataclasses.dataclass(frozen=True)

@@ -91,3 +91,4 @@ def _load_builtin() -> None:
         _LOADED = True
         from .models import qwen3  # noqa: F401  (registers itself)
         from .models import sanozen  # noqa: F401
+        from .models import gakenex  # noqa: F401
