@@ -342,3 +342,433 @@ KIDI_API int kidi_diff_attention_generic(const DiffAttentionArgs* args, int dtyp
     if (dtype == KIDI_BF16) return kidi_launch(diff_attention_generic_kernel<bf16>, grid, 128, 0, stream, a);
     return KIDI_REFUSED_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// The tensor-core kernels (bfloat16), compiled for one pair of widths.
+//
+// A block of four warps takes rows of one sequence that share a key/value head: in a prompt, 64 rows
+// = 64 / (heads per key/value head) consecutive tokens times those heads, a warp 16 rows and all 64
+// keys of a tile; with one token a sequence, the 16 (or fewer) heads of the token, each warp a
+// quarter of a tile's keys, merged through shared memory at the end. A tile is a 64-token page of
+// the cache (keys of both maps, values), copied with cp.async into one of two buffers while the
+// other is used. The tiles a block visits are the pages of its window and, before them, the pages
+// of the kept first tokens. Per map: S = Q K^T (mma.sync m16n8k16, fragments through ldmatrix), the
+// mask, an online softmax in 32-bit, P in bfloat16, O += P V. The two maps' sums stay in registers;
+// their difference, its norm and the gate are applied there too. With `splits` > 1 (one token a
+// sequence, long windows) the tiles of a (sequence, key/value head) are dealt to several blocks
+// whose results meet in a workspace and a second kernel.
+#if KIDI_DIFF_DIM > 0
+namespace tensor {
+
+constexpr int DIM = KIDI_DIFF_DIM, VDIM = KIDI_DIFF_VDIM;
+constexpr int KS = 2 * DIM + 8;      // elements between rows of a key or query tile in shared memory
+constexpr int VS = VDIM + 8;
+constexpr int TILE = 64;
+constexpr int NV = VDIM / 8;         // output column tiles
+constexpr int STAGE = VDIM + 4;      // floats between rows of the merge stage
+static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && DIM <= 128 && VDIM <= 128, "widths the kernel takes");
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t address = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t address = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void copy16(bf16* shared, const bf16* global) {
+    const uint32_t address = (uint32_t)__cvta_generic_to_shared(shared);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(global));
+}
+__device__ __forceinline__ uint32_t pack2(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// ROW_WARPS 4: prompts (64 rows a block); 1: one token a sequence (16 rows, the warps share a tile's keys).
+template <int ROW_WARPS>
+__global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentionArgs a) {
+    constexpr int KEY_WARPS = 4 / ROW_WARPS;
+    constexpr int ROWS = 16 * ROW_WARPS;
+    constexpr int KEYS_W = TILE / KEY_WARPS;
+    constexpr int NT = KEYS_W / 8;
+    extern __shared__ __align__(16) unsigned char shared_bytes[];
+    bf16* q_s = reinterpret_cast<bf16*>(shared_bytes);
+    bf16* k_s = q_s + ROWS * KS;
+    bf16* v_s = k_s + 2 * TILE * KS;
+
+    const DiffGeometry& g = a.geometry;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = g.heads / g.kv_heads;
+    const int seq = blockIdx.y, kv_head = blockIdx.z % g.kv_heads, split = blockIdx.z / g.kv_heads;
+    const int tokens = ROW_WARPS == 4 ? ROWS / group : 1;
+    const int len = a.tables.seq_len[seq], start = a.tables.seq_start[seq], row0 = a.tables.seq_row0[seq];
+    const int t0 = blockIdx.x * tokens;
+    if (t0 >= len) return;
+    const int live_tokens = min(tokens, len - t0), live_rows = live_tokens * group;
+    bf16* out = (bf16*)a.out;
+    if (a.tables.row_seq[row0] < 0) {          // a padding sequence of a captured step: zeros, nothing read
+        if (split == 0 && a.splits == 1)
+            for (int i = tid; i < live_rows * VDIM; i += 128) {
+                const int r = i / VDIM, c = i - r * VDIM;
+                out[((long long)(row0 + t0 + r / group) * g.heads + kv_head * group + r % group) * VDIM + c] =
+                    __float2bfloat16_rn(0.f);
+            }
+        return;
+    }
+    const int slot = a.tables.seq_slot[seq];
+    const int p_low = start + t0, p_high = start + t0 + live_tokens - 1;
+    const int low_page = a.window > 0 ? max(0, p_low - a.window + 1) >> 6 : 0;
+    const int high_page = p_high >> 6;
+    const int kept_tiles = min((a.keep_first + TILE - 1) >> 6, low_page);
+    const int tiles = kept_tiles + high_page - low_page + 1;
+    const int share = (tiles + a.splits - 1) / a.splits;
+    const int first_tile = split * share, end_tile = min(tiles, first_tile + share);
+
+    // The block's query rows: row r is token t0 + r / group, head kv_head * group + r % group.
+    const bf16* q = (const bf16*)a.q;
+    for (int i = tid; i < ROWS * (2 * DIM / 8); i += 128) {
+        const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (r < live_rows)
+            value = *reinterpret_cast<const uint4*>(
+                q + ((long long)(row0 + t0 + r / group) * g.heads + kv_head * group + r % group) * (2 * DIM) + piece * 8);
+        *reinterpret_cast<uint4*>(q_s + r * KS + piece * 8) = value;
+    }
+
+    const bf16* k_cache = (const bf16*)a.k_cache;
+    const bf16* v_cache = (const bf16*)a.v_cache;
+    const int* table = g.table + (long long)slot * g.pages_per_seq;
+    auto page_of = [&](int tile) { return tile < kept_tiles ? tile : low_page + tile - kept_tiles; };
+    auto load_tile = [&](int tile, int buffer) {
+        const long long at = ((long long)table[page_of(tile)] * g.kv_heads + kv_head) << 6;
+        const bf16* keys = k_cache + at * (2 * DIM);
+        const bf16* values = v_cache + at * VDIM;
+        bf16* k_to = k_s + buffer * TILE * KS;
+        bf16* v_to = v_s + buffer * TILE * VS;
+        for (int i = tid; i < TILE * (2 * DIM / 8); i += 128) {
+            const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
+            copy16(k_to + r * KS + piece * 8, keys + r * (2 * DIM) + piece * 8);
+        }
+        for (int i = tid; i < TILE * (VDIM / 8); i += 128) {
+            const int r = i / (VDIM / 8), piece = i - r * (VDIM / 8);
+            copy16(v_to + r * VS + piece * 8, values + r * VDIM + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+
+    const int row_warp = warp / KEY_WARPS, key0 = (warp % KEY_WARPS) * KEYS_W;
+    const int row_a = row_warp * 16 + (lane >> 2), row_b = row_a + 8;
+    // A row's position; -1 for rows beyond the block's live rows: they see nothing.
+    const int pos_a = row_a < live_rows ? start + t0 + row_a / group : -1;
+    const int pos_b = row_b < live_rows ? start + t0 + row_b / group : -1;
+    const float scale_log2 = a.scale * 1.4426950408889634f;
+
+    float o[2][NV][4];
+    float top_a[2] = {-INFINITY, -INFINITY}, top_b[2] = {-INFINITY, -INFINITY};
+    float sum_a[2] = {0.f, 0.f}, sum_b[2] = {0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NV; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
+
+    if (first_tile < end_tile) load_tile(first_tile, 0);
+    for (int tile = first_tile; tile < end_tile; ++tile) {
+        const int buffer = (tile - first_tile) & 1;
+        if (tile + 1 < end_tile) {
+            load_tile(tile + 1, buffer ^ 1);
+            asm volatile("cp.async.wait_group 1;");
+        } else {
+            asm volatile("cp.async.wait_group 0;");
+        }
+        __syncthreads();
+        const bf16* k_tile = k_s + buffer * TILE * KS;
+        const bf16* v_tile = v_s + buffer * TILE * VS;
+        const int key_base = (page_of(tile) << 6) + key0;
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float s[NT][4];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < DIM / 16; ++ks) {
+                uint32_t qa[4];
+                ldmatrix_x4(qa, q_s + (row_warp * 16 + (lane & 15)) * KS + m * DIM + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int n2 = 0; n2 < NT / 2; ++n2) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, k_tile + (key0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + m * DIM + ks * 16 +
+                                        ((lane >> 3) & 1) * 8);
+                    mma_bf16(s[2 * n2], qa, kb[0], kb[1]);
+                    mma_bf16(s[2 * n2 + 1], qa, kb[2], kb[3]);
+                }
+            }
+            float most_a = -INFINITY, most_b = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int u = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
+                    const int p = e < 2 ? pos_a : pos_b;
+                    const bool seen = u <= p && (a.window <= 0 || p - u < a.window || u < a.keep_first);
+                    const float value = seen ? s[n][e] * scale_log2 : -INFINITY;
+                    s[n][e] = value;
+                    if (e < 2) most_a = fmaxf(most_a, value); else most_b = fmaxf(most_b, value);
+                }
+            const float next_a = fmaxf(top_a[m], quad_max(most_a)), next_b = fmaxf(top_b[m], quad_max(most_b));
+            const float base_a = next_a == -INFINITY ? 0.f : next_a, base_b = next_b == -INFINITY ? 0.f : next_b;
+            const float keep_a = exp2f(top_a[m] - base_a), keep_b = exp2f(top_b[m] - base_b);
+            top_a[m] = next_a;
+            top_b[m] = next_b;
+            float add_a = 0.f, add_b = 0.f;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                s[n][0] = exp2f(s[n][0] - base_a); s[n][1] = exp2f(s[n][1] - base_a);
+                s[n][2] = exp2f(s[n][2] - base_b); s[n][3] = exp2f(s[n][3] - base_b);
+                add_a += s[n][0] + s[n][1];
+                add_b += s[n][2] + s[n][3];
+            }
+            sum_a[m] = sum_a[m] * keep_a + add_a;
+            sum_b[m] = sum_b[m] * keep_b + add_b;
+#pragma unroll
+            for (int n = 0; n < NV; ++n) {
+                o[m][n][0] *= keep_a; o[m][n][1] *= keep_a;
+                o[m][n][2] *= keep_b; o[m][n][3] *= keep_b;
+            }
+#pragma unroll
+            for (int kk = 0; kk < KEYS_W / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack2(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < NV / 2; ++n2) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, v_tile + (key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + n2 * 16 +
+                                              (lane >> 4) * 8);
+                    mma_bf16(o[m][2 * n2], pa, vb[0], vb[1]);
+                    mma_bf16(o[m][2 * n2 + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        sum_a[m] = quad_sum(sum_a[m]);
+        sum_b[m] = quad_sum(sum_b[m]);
+    }
+
+    if (KEY_WARPS > 1) {
+        // The four warps hold the same 16 rows over different keys: they meet in shared memory, behind the
+        // query rows, and the first warp adds them up.
+        float* stage = reinterpret_cast<float*>(shared_bytes + ((ROWS * KS * 2 + 15) & ~15));   // [4][2][16][STAGE]
+        float* stats = stage + 4 * 2 * 16 * STAGE;                                               // [4][2][16][2]
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float* mine = stage + ((warp * 2 + m) * 16) * STAGE;
+#pragma unroll
+            for (int n = 0; n < NV; ++n) {
+                const int c = n * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(mine + (lane >> 2) * STAGE + c) = make_float2(o[m][n][0], o[m][n][1]);
+                *reinterpret_cast<float2*>(mine + ((lane >> 2) + 8) * STAGE + c) = make_float2(o[m][n][2], o[m][n][3]);
+            }
+            if ((lane & 3) == 0) {
+                float* at = stats + ((warp * 2 + m) * 16) * 2;
+                at[(lane >> 2) * 2] = top_a[m]; at[(lane >> 2) * 2 + 1] = sum_a[m];
+                at[((lane >> 2) + 8) * 2] = top_b[m]; at[((lane >> 2) + 8) * 2 + 1] = sum_b[m];
+            }
+        }
+        __syncthreads();
+        if (warp) return;
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float best_a = -INFINITY, best_b = -INFINITY;
+            for (int w = 0; w < 4; ++w) {
+                const float* at = stats + ((w * 2 + m) * 16) * 2;
+                best_a = fmaxf(best_a, at[(lane >> 2) * 2]);
+                best_b = fmaxf(best_b, at[((lane >> 2) + 8) * 2]);
+            }
+            float total_a = 0.f, total_b = 0.f;
+#pragma unroll
+            for (int n = 0; n < NV; ++n) o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.f;
+            for (int w = 0; w < 4; ++w) {
+                const float* at = stats + ((w * 2 + m) * 16) * 2;
+                const float has_a = at[(lane >> 2) * 2], has_b = at[((lane >> 2) + 8) * 2];
+                const float factor_a = has_a == -INFINITY ? 0.f : exp2f(has_a - best_a);
+                const float factor_b = has_b == -INFINITY ? 0.f : exp2f(has_b - best_b);
+                total_a += at[(lane >> 2) * 2 + 1] * factor_a;
+                total_b += at[((lane >> 2) + 8) * 2 + 1] * factor_b;
+                const float* theirs = stage + ((w * 2 + m) * 16) * STAGE;
+#pragma unroll
+                for (int n = 0; n < NV; ++n) {
+                    const int c = n * 8 + (lane & 3) * 2;
+                    const float2 upper = *reinterpret_cast<const float2*>(theirs + (lane >> 2) * STAGE + c);
+                    const float2 lower = *reinterpret_cast<const float2*>(theirs + ((lane >> 2) + 8) * STAGE + c);
+                    o[m][n][0] += upper.x * factor_a; o[m][n][1] += upper.y * factor_a;
+                    o[m][n][2] += lower.x * factor_b; o[m][n][3] += lower.y * factor_b;
+                }
+            }
+            top_a[m] = best_a; top_b[m] = best_b;
+            sum_a[m] = total_a; sum_b[m] = total_b;
+        }
+    }
+
+    // Each map's weighted sum divided by its softmax sum (a row without a key, which only a share of
+    // the tiles can be, gives zeros and a zero sum).
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        const float inv_a = sum_a[m] > 0.f ? 1.0f / sum_a[m] : 0.f, inv_b = sum_b[m] > 0.f ? 1.0f / sum_b[m] : 0.f;
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            o[m][n][0] *= inv_a; o[m][n][1] *= inv_a;
+            o[m][n][2] *= inv_b; o[m][n][3] *= inv_b;
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = half ? row_b : row_a;
+        const bool live = r < live_rows;
+        const long long row = row0 + t0 + (live ? r / group : 0);
+        const int head = kv_head * group + (live ? r % group : 0);
+        if (a.splits > 1) {
+            if (live) {
+                float* to = a.partial + ((row * g.heads + head) * a.splits + split) * (2 * VDIM + 4);
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int n = 0; n < NV; ++n)
+                        *reinterpret_cast<float2*>(to + m * VDIM + n * 8 + (lane & 3) * 2) =
+                            make_float2(o[m][n][2 * half], o[m][n][2 * half + 1]);
+                if ((lane & 3) == 0) {
+                    to[2 * VDIM] = half ? top_b[0] : top_a[0]; to[2 * VDIM + 1] = half ? sum_b[0] : sum_a[0];
+                    to[2 * VDIM + 2] = half ? top_b[1] : top_a[1]; to[2 * VDIM + 3] = half ? sum_b[1] : sum_a[1];
+                }
+            }
+            continue;
+        }
+        float square = 0.f;
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const float x = o[0][n][2 * half] - a.lambda * o[1][n][2 * half];
+            const float y = o[0][n][2 * half + 1] - a.lambda * o[1][n][2 * half + 1];
+            o[0][n][2 * half] = x;
+            o[0][n][2 * half + 1] = y;
+            square = fmaf(x, x, fmaf(y, y, square));
+        }
+        const float inv = 1.0f / sqrtf(quad_sum(square) / (float)VDIM + a.eps) * a.post_scale;
+        if (!live) continue;
+        bf16* to = out + (row * g.heads + head) * VDIM;
+        const bf16* gate = a.gate ? (const bf16*)a.gate + row * a.ldg + (long long)head * VDIM : nullptr;
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int c = n * 8 + (lane & 3) * 2;
+            float x = o[0][n][2 * half] * inv, y = o[0][n][2 * half + 1] * inv;
+            if (gate) {
+                const float2 opened = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + c));
+                x *= 1.0f / (1.0f + expf(-opened.x));
+                y *= 1.0f / (1.0f + expf(-opened.y));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(to + c) = __floats2bfloat162_rn(x, y);
+        }
+    }
+}
+
+// The shares of a (row, head) meet: a warp a (row, head).
+__global__ void __launch_bounds__(128) diff_combine_kernel(DiffAttentionArgs a) {
+    const DiffGeometry& g = a.geometry;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)a.rows * g.heads) return;
+    const int row = (int)(item / g.heads), head = (int)(item - (long long)row * g.heads);
+    if (a.tables.row_seq[row] < 0) {
+        bf16* out = (bf16*)a.out + ((long long)row * g.heads + head) * VDIM;
+        for (int c = lane; c < VDIM; c += 32) out[c] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const float* from = a.partial + item * a.splits * (2 * VDIM + 4);
+    float o[2][8];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        float best = -INFINITY;
+        for (int s = 0; s < a.splits; ++s) best = fmaxf(best, from[s * (2 * VDIM + 4) + 2 * VDIM + 2 * m]);
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[m][i] = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float* share = from + s * (2 * VDIM + 4);
+            const float has = share[2 * VDIM + 2 * m], sum = share[2 * VDIM + 2 * m + 1];
+            const float factor = (has == -INFINITY || sum <= 0.f) ? 0.f : sum * exp2f(has - best);
+            total += factor;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (lane + 32 * i < VDIM) o[m][i] += share[m * VDIM + lane + 32 * i] * factor;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[m][i] /= total;
+    }
+    diff_finish<bf16>(a, row, head, lane, o[0], o[1]);
+}
+
+}  // namespace tensor
+
+KIDI_API int kidi_diff_attention_tensor(const DiffAttentionArgs* args, cudaStream_t stream) {
+    using namespace tensor;
+    const DiffAttentionArgs& a = *args;
+    const DiffGeometry& g = a.geometry;
+    if (a.rows <= 0) return 0;
+    if (g.dim != DIM || g.vdim != VDIM || g.page_shift != 6 || g.heads % g.kv_heads || a.splits < 1) return KIDI_REFUSED_SIZE;
+    const int group = g.heads / g.kv_heads;
+    const bool one_token = a.max_new == 1;
+    if (group > (one_token ? 16 : 64) || a.seqs > 65535 || (long long)g.kv_heads * a.splits > 65535) return KIDI_REFUSED_SIZE;
+    if (a.splits > 1 && (!one_token || !a.partial)) return KIDI_REFUSED_SIZE;
+    const size_t tiles = (size_t)(2 * TILE * KS + 2 * TILE * VS) * sizeof(bf16);
+    int status;
+    if (one_token) {
+        const size_t rows = ((size_t)16 * KS * sizeof(bf16) + 15) & ~(size_t)15;
+        const size_t stage = (size_t)(4 * 2 * 16 * STAGE + 4 * 2 * 16 * 2) * sizeof(float);
+        const size_t shared = rows + (tiles > stage ? tiles : stage);
+        static bool set = false;
+        if (!set) {
+            cudaError_t error = cudaFuncSetAttribute(diff_attention_tensor_kernel<1>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+            if (error != cudaSuccess) return (int)error;
+            set = true;
+        }
+        status = kidi_launch(diff_attention_tensor_kernel<1>, dim3(1, a.seqs, g.kv_heads * a.splits), 128, shared, stream, a);
+        if (status || a.splits == 1) return status;
+        const long long items = (long long)a.rows * g.heads;
+        return kidi_launch(diff_combine_kernel, (unsigned)((items + 3) / 4), 128, 0, stream, a);
+    }
+    const size_t shared = (size_t)64 * KS * sizeof(bf16) + tiles;
+    static bool set = false;
+    if (!set) {
+        cudaError_t error = cudaFuncSetAttribute(diff_attention_tensor_kernel<4>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (error != cudaSuccess) return (int)error;
+        set = true;
+    }
+    const int tokens = 64 / group;
+    return kidi_launch(diff_attention_tensor_kernel<4>, dim3((a.max_new + tokens - 1) / tokens, a.seqs, g.kv_heads), 128,
+                       shared, stream, a);
+}
+#endif

@@ -14,8 +14,7 @@ from ..errors import invalid_argument
 from . import ops
 from .ops import _check, c_float, c_int, c_longlong, c_void_p, dtype_code
 
-FORCE_GENERAL = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1" or \
-    os.environ.get("KIDI_B200_DIFF_TENSOR", "0") != "1"
+FORCE_GENERAL = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
 MAX_TAPS = 8
 
 
@@ -139,12 +138,14 @@ def attention(ctx, q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
                              kv_view.values.data_ptr(), _geometry(kv_view, heads, kv_heads, dim, vdim),
                              _tables(ctx.tables), out.data_ptr(), rows, plan.n_seqs, plan.max_new, int(window or 0),
                              int(keep_first), float(scale), float(lam), float(post_scale), float(eps), 0, 1)
-    if general or not tensor_fits(q.dtype, dim, vdim, kv_view.page_size):
+    group = heads // kv_heads
+    if general or not tensor_fits(q.dtype, dim, vdim, kv_view.page_size) or group > (16 if plan.is_decode else 64) \
+            or (gate is not None and (gate.stride(0) % 2 or gate.data_ptr() % 4)):
         _check(library().kidi_diff_attention_generic(ctypes.byref(args), dtype_code(q.dtype), ops._stream()),
                "diff_attention")
         return
     reach = plan.max_total if not window else min(plan.max_total, int(window) + int(keep_first) + 64)
-    splits = tensor_splits(rows, plan.n_seqs, plan.max_new, heads, kv_heads, reach, q.device) if plan.is_decode else 1
+    splits = tensor_splits(plan.n_seqs, kv_heads, reach, q.device) if plan.is_decode else 1
     if splits > 1:
         args.partial = ctx.workspace("diff_attention_partial", rows * heads * splits * (2 * vdim + 4)).data_ptr()
         args.splits = splits
@@ -152,8 +153,7 @@ def attention(ctx, q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
            f"diff_attention[tensor{', split' if splits > 1 else ''}]", 2 if splits > 1 else 1)
 
 
-def tensor_splits(rows: int, seqs: int, max_new: int, heads: int, kv_heads: int, reach: int,
-                  device: torch.device) -> int:
+def tensor_splits(seqs: int, kv_heads: int, reach: int, device: torch.device) -> int:
     """How many blocks share the keys of a (sequence, key/value head) when every sequence brings one token:
     enough to fill the SMs, at most one per two pages of 64 keys."""
     from .attention import sm_count

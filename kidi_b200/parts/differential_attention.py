@@ -110,6 +110,18 @@ class DifferentialAttention(Part):
             requests.append(StateRequest((self.taps - 1, self.channels)))
         return requests
 
+    def launch_signature(self, rows: int, longest: int) -> tuple:
+        """What a captured decode step freezes of this part's launches: the key splits of the tensor-core kernel."""
+        if not differential.tensor_fits(self.env.dtype, self.dim, self.vdim, 64):
+            return ()
+        return (differential.tensor_splits(rows, self.kv_heads, self._reach(longest), self.env.device),)
+
+    def _reach(self, longest: int) -> int:
+        """The most keys a row of a sequence of `longest` tokens reads."""
+        if self.window is None:
+            return longest
+        return min(longest, int(self.window) + self.keep_first + 64)
+
     def forward(self, x, ctx, views, owns_cache: bool) -> torch.Tensor:
         if not owns_cache:
             raise unsupported("a differential attention layer keeps its own keys, values and convolution state")
