@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--model 8b|14b|32b] [--impl ours|reference]
-    python bench.py --design sanozen [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
+    python bench.py --design sanozen|gakenex [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
 
 A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
 layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
@@ -309,6 +309,27 @@ def sanozen_shape(width: int, layers: int = 4) -> dict:
             "norm": {"eps": 1e-5}, "token_side": {"dim": 64}, "layers": stack, "max_positions": 8192}
 
 
+def gakenex_shape(width: int, layers: int = 4) -> dict:
+    """A Gakenex stack at the layer sizes of a model of `width`: heads with two maps of 64 and values of 128, a
+    key/value head for four heads, four convolution taps, a window of 4,096 with four kept tokens; dense
+    feed-forwards of the Qwen3 layers' size in turn with routed ones (16 experts, two a token, each half that
+    size, so that a token uses as many weights)."""
+    heads = width // 128
+    inter = (8 * width // 3 + 127) // 128 * 128
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6,
+             "scale": 64 ** -0.5, "mask": {"size": 4096, "keep_first": 4}}
+    stack = []
+    for index in range(layers):
+        mlp = {"kind": "dense", "ff": inter, "limit": 7.0} if index % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": inter // 2}, "router": {"experts": 16, "top": 2}}
+        stack.append({"type": "attention", "mixer": dict(mixer), "mlp": mlp})
+    return {"architecture": "Gakenex", "vocab": 32768, "width": width, "max_positions": 8192, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "layers": stack}
+
+
+DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape}
+
+
 def qwen3_shape(width: int, layers: int = 4) -> dict:
     """The closest existing model at equal size: Qwen3 layers of the same width and head count (a key/value head for
     four heads) whose gated feed-forward has as many weights as the dense one of 4 width."""
@@ -324,18 +345,21 @@ KERNEL_CLASSES = (
     ("decode attention", ("attention_decode", "latent_attention")),
     ("recurrence", ("gated_recurrence",)),
     ("stream norm", ("add_rmsnorm", "add_layernorm")),
-    ("activation", ("silu_gate", "poly_norm")),
+    ("activation", ("silu_gate", "poly_norm", "bounded_gate")),
+    ("experts through the choice", ("expert_slots",)),
 )
 
 
-def kernel_class(name: str) -> str:
+def kernel_class(name: str, decode: bool = False) -> str:
+    if name.startswith("diff_attention"):
+        return "decode attention" if decode else "prompt attention"
     for label, prefixes in KERNEL_CLASSES:
         if name.startswith(prefixes):
             return label
     return "other row-wise kernels"
 
 
-def timed_step(engine, slots, tokens) -> dict:
+def timed_step(engine, slots, tokens, decode: bool = False) -> dict:
     """One `Engine.step` with every launch timed on the device: microseconds and launches per class of kernel."""
     from kidi_b200 import StepBatch
     from kidi_b200.kernels import ops
@@ -343,7 +367,7 @@ def timed_step(engine, slots, tokens) -> dict:
         engine.step(StepBatch(slots, tokens, None))
     classes: dict = {}
     for name, microseconds in timed.spans():
-        entry = classes.setdefault(kernel_class(name), {"us": 0.0, "launches": 0, "kernels": {}})
+        entry = classes.setdefault(kernel_class(name, decode), {"us": 0.0, "launches": 0, "kernels": {}})
         entry["us"] += microseconds
         entry["launches"] += 1
         kernel = entry["kernels"].setdefault(name.split(",")[0], [0, 0.0])
@@ -366,6 +390,30 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
         norms, act_width = 2 * layers + 1, layers * inter * 3          # gate and up read, the product written
         work["prompt attention"] = ("flops", layers * 4.0 * heads * hd * rows * (rows + 1) / 2)
         work["decode attention"] = ("bytes", layers * rows * context * kv * hd * 2 * 2.0)
+    elif design == "gakenex":
+        width, layers = config["width"], config["layers"]
+        weights, norms, act_width, attention, cache, chosen = config["vocab"] * width, 2, 0, 0.0, 0.0, 0.0
+        for layer in layers:
+            m, mlp = layer["mixer"], layer["mlp"]
+            heads, groups, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            weights += width * (2 * (heads + groups) * dim + groups * vdim + heads * vdim) + heads * vdim * width
+            norms += 1
+            attention += 4.0 * heads * (dim + vdim) * rows * (rows + 1) / 2      # two maps: scores of dim, sums of vdim
+            cache += rows * context * groups * (2 * dim + vdim) * 2.0
+            if mlp["kind"] == "dense":
+                weights += 3 * width * mlp["ff"]
+                act_width += 3 * mlp["ff"]
+            else:
+                used = 3 * width * mlp["expert"]["ff"] * mlp["router"]["top"]        # per token
+                if decode:     # each (row, choice) streams its expert's weights (rows * top <= experts here)
+                    chosen += rows * used * 2.0
+                else:
+                    weights += used
+                    act_width += 3 * mlp["expert"]["ff"] * mlp["router"]["top"]
+        work["prompt attention"] = ("flops", attention)
+        work["decode attention"] = ("bytes", cache)
+        if decode:
+            work["experts through the choice"] = ("bytes", chosen)
     else:
         width, layers = config["width"], config["layers"]
         weights, norms, act_width, attention, cache, scan_flops, scan_bytes, state = config["vocab"] * width, 1, 0, 0.0, 0.0, 0.0, 0.0, 0.0
@@ -399,8 +447,8 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
 
 
 def design_comparison(args) -> int:
-    """`--design sanozen`: prompts and decoding of a Sanozen stack beside Qwen3 layers of equal size, with every
-    class of kernel against its roofline."""
+    """`--design sanozen` / `--design gakenex`: prompts and decoding of a stack of that design beside Qwen3 layers
+    of equal size, with every class of kernel against its roofline."""
     import torch
     from kidi_b200 import Engine
     from kidi_b200.sampling.sampler import Sampler
@@ -411,7 +459,8 @@ def design_comparison(args) -> int:
     sizes = []
     for width in [int(value) for value in args.widths.split(",")]:
         point = {"width": width}
-        for design, shape in (("sanozen", sanozen_shape(width, args.layers or 4)), ("qwen3", qwen3_shape(width, args.layers or 4))):
+        for design, shape in ((args.design, DESIGN_SHAPES[args.design](width, args.layers or 4)),
+                              ("qwen3", qwen3_shape(width, args.layers or 4))):
             engine = Engine.from_config(shape, seed=args.seed, dtype="bfloat16", device="cuda:0",
                                         max_tokens=max(batch * (context + steps + 64 + args.warmup), 4096))
             from kidi_b200 import StepBatch
@@ -428,7 +477,7 @@ def design_comparison(args) -> int:
             slots = [engine.acquire() for _ in range(batch)]
             engine.step(StepBatch(slots, prompts, None))
             engine.step(StepBatch(slots, [[1]] * batch, None))           # every decode kernel is built and configured
-            decode_classes = timed_step(engine, slots, [[2]] * batch)
+            decode_classes = timed_step(engine, slots, [[2]] * batch, decode=True)
             for used in slots:
                 engine.release(used)
             for classes, decode in ((prompt_classes, False), (decode_classes, True)):
@@ -448,7 +497,7 @@ def design_comparison(args) -> int:
             torch.cuda.empty_cache()
         sizes.append(point)
     print(json.dumps({
-        "metric": f"prefill and decode tokens/s of a Sanozen stack beside Qwen3 layers of equal size (bf16, "
+        "metric": f"prefill and decode tokens/s of a {args.design.capitalize()} stack beside Qwen3 layers of equal size (bf16, "
                   f"{args.layers or 4} layers, one {PREFILL_TOKENS}-token prompt; batch {batch} decoding at {context} tokens)",
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16", "impl": "ours",
         "data": "synthetic: random weights from a seed, uniform token ids", "peaks": peak, "sizes": sizes,
@@ -460,8 +509,8 @@ def design_comparison(args) -> int:
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--design", default="", choices=["", "sanozen"],
-                        help="sanozen: a Sanozen stack beside Qwen3 layers of equal size, kernel class by kernel class "
+    parser.add_argument("--design", default="", choices=["", "sanozen", "gakenex"],
+                        help="a Sanozen or Gakenex stack beside Qwen3 layers of equal size, kernel class by kernel class "
                              "(the default workload is left as it is)")
     parser.add_argument("--widths", default="2048,4096", help="model widths of --design runs")
     parser.add_argument("--gpus", type=int, default=1)

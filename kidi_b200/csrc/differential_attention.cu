@@ -392,6 +392,11 @@ __device__ __forceinline__ uint32_t pack2(float low, float high) {
     const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<const uint32_t*>(&pair);
 }
+__device__ __forceinline__ float exp2_fast(float v) {        // 2^v; 0 for -inf
+    float result;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(result) : "f"(v));
+    return result;
+}
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -419,7 +424,8 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
     const int seq = blockIdx.y, kv_head = blockIdx.z % g.kv_heads, split = blockIdx.z / g.kv_heads;
     const int tokens = ROW_WARPS == 4 ? ROWS / group : 1;
     const int len = a.tables.seq_len[seq], start = a.tables.seq_start[seq], row0 = a.tables.seq_row0[seq];
-    const int t0 = blockIdx.x * tokens;
+    // the blocks with the most keys to walk (a sequence's last tokens) start first
+    const int t0 = (gridDim.x - 1 - blockIdx.x) * tokens;
     if (t0 >= len) return;
     const int live_tokens = min(tokens, len - t0), live_rows = live_tokens * group;
     bf16* out = (bf16*)a.out;
@@ -440,17 +446,6 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
     const int tiles = kept_tiles + high_page - low_page + 1;
     const int share = (tiles + a.splits - 1) / a.splits;
     const int first_tile = split * share, end_tile = min(tiles, first_tile + share);
-
-    // The block's query rows: row r is token t0 + r / group, head kv_head * group + r % group.
-    const bf16* q = (const bf16*)a.q;
-    for (int i = tid; i < ROWS * (2 * DIM / 8); i += 128) {
-        const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
-        uint4 value = make_uint4(0u, 0u, 0u, 0u);
-        if (r < live_rows)
-            value = *reinterpret_cast<const uint4*>(
-                q + ((long long)(row0 + t0 + r / group) * g.heads + kv_head * group + r % group) * (2 * DIM) + piece * 8);
-        *reinterpret_cast<uint4*>(q_s + r * KS + piece * 8) = value;
-    }
 
     const bf16* k_cache = (const bf16*)a.k_cache;
     const bf16* v_cache = (const bf16*)a.v_cache;
@@ -491,6 +486,17 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
             for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
 
     if (first_tile < end_tile) load_tile(first_tile, 0);
+    // The block's query rows (while the first tile is on its way): row r is token t0 + r / group, head
+    // kv_head * group + r % group.
+    const bf16* q = (const bf16*)a.q;
+    for (int i = tid; i < ROWS * (2 * DIM / 8); i += 128) {
+        const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (r < live_rows)
+            value = *reinterpret_cast<const uint4*>(
+                q + ((long long)(row0 + t0 + r / group) * g.heads + kv_head * group + r % group) * (2 * DIM) + piece * 8);
+        *reinterpret_cast<uint4*>(q_s + r * KS + piece * 8) = value;
+    }
     for (int tile = first_tile; tile < end_tile; ++tile) {
         const int buffer = (tile - first_tile) & 1;
         if (tile + 1 < end_tile) {
@@ -502,7 +508,10 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
         __syncthreads();
         const bf16* k_tile = k_s + buffer * TILE * KS;
         const bf16* v_tile = v_s + buffer * TILE * VS;
-        const int key_base = (page_of(tile) << 6) + key0;
+        const int tile_key = page_of(tile) << 6, key_base = tile_key + key0;
+        // A tile that every row of the block sees whole needs no mask (most tiles of a long sequence).
+        const bool whole = tile_key + TILE - 1 <= p_low &&
+                           (a.window <= 0 || p_high - tile_key < a.window || tile_key + TILE - 1 < a.keep_first);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             float s[NT][4];
@@ -521,28 +530,35 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
                     mma_bf16(s[2 * n2 + 1], qa, kb[2], kb[3]);
                 }
             }
+            // Scores stay unscaled; the scale (times log2 e) enters the exponent's multiply-add.
             float most_a = -INFINITY, most_b = -INFINITY;
+            if (!whole) {
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
+                for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int u = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
-                    const int p = e < 2 ? pos_a : pos_b;
-                    const bool seen = u <= p && (a.window <= 0 || p - u < a.window || u < a.keep_first);
-                    const float value = seen ? s[n][e] * scale_log2 : -INFINITY;
-                    s[n][e] = value;
-                    if (e < 2) most_a = fmaxf(most_a, value); else most_b = fmaxf(most_b, value);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const int u = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
+                        const int p = e < 2 ? pos_a : pos_b;
+                        const bool seen = u <= p && (a.window <= 0 || p - u < a.window || u < a.keep_first);
+                        if (!seen) s[n][e] = -INFINITY;
+                    }
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                most_a = fmaxf(most_a, fmaxf(s[n][0], s[n][1]));
+                most_b = fmaxf(most_b, fmaxf(s[n][2], s[n][3]));
+            }
             const float next_a = fmaxf(top_a[m], quad_max(most_a)), next_b = fmaxf(top_b[m], quad_max(most_b));
-            const float base_a = next_a == -INFINITY ? 0.f : next_a, base_b = next_b == -INFINITY ? 0.f : next_b;
-            const float keep_a = exp2f(top_a[m] - base_a), keep_b = exp2f(top_b[m] - base_b);
+            const float base_a = next_a == -INFINITY ? 0.f : next_a * scale_log2;
+            const float base_b = next_b == -INFINITY ? 0.f : next_b * scale_log2;
+            const float keep_a = exp2_fast(top_a[m] * scale_log2 - base_a), keep_b = exp2_fast(top_b[m] * scale_log2 - base_b);
             top_a[m] = next_a;
             top_b[m] = next_b;
             float add_a = 0.f, add_b = 0.f;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                s[n][0] = exp2f(s[n][0] - base_a); s[n][1] = exp2f(s[n][1] - base_a);
-                s[n][2] = exp2f(s[n][2] - base_b); s[n][3] = exp2f(s[n][3] - base_b);
+                s[n][0] = exp2_fast(fmaf(s[n][0], scale_log2, -base_a)); s[n][1] = exp2_fast(fmaf(s[n][1], scale_log2, -base_a));
+                s[n][2] = exp2_fast(fmaf(s[n][2], scale_log2, -base_b)); s[n][3] = exp2_fast(fmaf(s[n][3], scale_log2, -base_b));
                 add_a += s[n][0] + s[n][1];
                 add_b += s[n][2] + s[n][3];
             }
@@ -576,6 +592,8 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
     for (int m = 0; m < 2; ++m) {
         sum_a[m] = quad_sum(sum_a[m]);
         sum_b[m] = quad_sum(sum_b[m]);
+        top_a[m] *= scale_log2;           // from here on the largest scores are exponents of two (-inf stays)
+        top_b[m] *= scale_log2;
     }
 
     if (KEY_WARPS > 1) {

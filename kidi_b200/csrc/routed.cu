@@ -9,7 +9,7 @@
 // A (row, choice) pair is a "slot": slot = row * top + choice.
 //
 // Kernels:
-//  * choose: scores, the top choices and their weights, a warp a row;
+//  * choose: the router's product, the scores, the top choices and their weights, a block a row;
 //  * slots, gate and up: for few rows, and for every row count of the 32-bit engine: a warp per
 //    (slot, feature) reads the chosen expert's two weight rows once and applies the activation; the
 //    input weight is applied to the two products in 32-bit (W (w h) = w (W h));
@@ -22,17 +22,49 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- choose
-// logits [rows, experts] float; a warp a row; scores staged in shared memory (experts <= 1024).
-__global__ void __launch_bounds__(128) route_choose_kernel(const float* __restrict__ logits, int* __restrict__ chosen,
-                                                           float* __restrict__ weight, int rows, int experts, int top,
-                                                           int renormalise) {
-    extern __shared__ float staged[];
+// One row of weights against one row of x, a warp's share; the caller sums over the warp.
+template <typename T, typename TW>
+__device__ __forceinline__ float dot1(const TW* __restrict__ w, const T* __restrict__ x, int K, int lane) {
+    float a = 0.f;
+    for (int k = lane; k < K; k += 32) a = fmaf(to_float(w[k]), to_float(x[k]), a);
+    return a;
+}
+template <>
+__device__ __forceinline__ float dot1<bf16, bf16>(const bf16* __restrict__ w, const bf16* __restrict__ x, int K, int lane) {
+    float a = 0.f;
+    if ((K & 7) || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) {
+        for (int k = lane; k < K; k += 32) a = fmaf(to_float(w[k]), to_float(x[k]), a);
+        return a;
+    }
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 rw = *reinterpret_cast<const uint4*>(w + k), rx = *reinterpret_cast<const uint4*>(x + k);
+        const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&rw);
+        const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&rx);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fw = __bfloat1622float2(pw[i]), fx = __bfloat1622float2(px[i]);
+            a = fmaf(fw.x, fx.x, a);
+            a = fmaf(fw.y, fx.y, a);
+        }
+    }
+    return a;
+}
+
+// A block a row: its sixteen warps share the experts (a warp a router row at a time, 32-bit sums in an order
+// that depends on the width only), then the first warp takes the `top` largest scores, one after the other.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(512) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
+                                                    int* __restrict__ chosen, float* __restrict__ weight, int hidden,
+                                                    int experts, int top, int renormalise) {
+    extern __shared__ float score[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + warp;
-    if (row >= rows) return;
-    float* score = staged + (long long)warp * experts;
-    for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-logits[(long long)row * experts + e]));
-    __syncwarp();
+    const long long row = blockIdx.x;
+    for (int e = warp; e < experts; e += 16) {
+        const float z = warp_sum(dot1<T, TW>(router + (long long)e * hidden, x + row * hidden, hidden, lane));
+        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
+    }
+    __syncthreads();
+    if (warp) return;
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -47,24 +79,33 @@ __global__ void __launch_bounds__(128) route_choose_kernel(const float* __restri
             const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
             if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
         }
-        if (at == 0x7fffffff) at = 0;                     // every score a NaN
+        if (at == 0x7fffffff) at = k;                     // every score left is a NaN
         if (lane == 0) {
-            chosen[(long long)row * top + k] = at;
-            weight[(long long)row * top + k] = best;
+            chosen[row * top + k] = at;
+            weight[row * top + k] = best;
             score[at] = -INFINITY;
         }
         total += best;
         __syncwarp();
     }
-    if (renormalise && lane < top) weight[(long long)row * top + lane] /= total;
+    if (renormalise && lane < top) weight[row * top + lane] /= total;
 }
 
-KIDI_API int kidi_route_choose(const float* logits, int* chosen, float* weight, int rows, int experts, int top,
-                               int renormalise, cudaStream_t stream) {
+KIDI_API int kidi_route(const void* x, int dtype, const void* router, int weight_dtype, int* chosen, float* weight,
+                        int rows, int hidden, int experts, int top, int renormalise, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32) return KIDI_REFUSED_SIZE;
-    return kidi_launch(route_choose_kernel, (unsigned)((rows + 3) / 4), 128, (size_t)4 * experts * sizeof(float), stream,
-                       logits, chosen, weight, rows, experts, top, renormalise);
+    const size_t shared = (size_t)experts * sizeof(float);
+#define KIDI_CASE(D, T, W, TW)                                                                                        \
+    if (dtype == D && weight_dtype == W)                                                                              \
+        return kidi_launch(route_kernel<T, TW>, (unsigned)rows, 512, shared, stream, (const T*)x, (const TW*)router,  \
+                           chosen, weight, hidden, experts, top, renormalise);
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
+#undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
 }
 
 // ------------------------------------------------------------------ dots

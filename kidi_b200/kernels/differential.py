@@ -139,7 +139,8 @@ def attention(ctx, q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
                              _tables(ctx.tables), out.data_ptr(), rows, plan.n_seqs, plan.max_new, int(window or 0),
                              int(keep_first), float(scale), float(lam), float(post_scale), float(eps), 0, 1)
     group = heads // kv_heads
-    if general or not tensor_fits(q.dtype, dim, vdim, kv_view.page_size) or group > (16 if plan.is_decode else 64) \
+    if general or scale <= 0 or not tensor_fits(q.dtype, dim, vdim, kv_view.page_size) \
+            or group > (16 if plan.is_decode else 64) \
             or (gate is not None and (gate.stride(0) % 2 or gate.data_ptr() % 4)):
         _check(library().kidi_diff_attention_generic(ctypes.byref(args), dtype_code(q.dtype), ops._stream()),
                "diff_attention")
@@ -162,5 +163,5 @@ def tensor_splits(seqs: int, kv_heads: int, reach: int, device: torch.device) ->
     if forced:
         return max(1, min(pages, forced))
     items = max(1, seqs * kv_heads)
-    wanted = max(1, (2 * sm_count(device)) // items)
+    wanted = max(1, (3 * sm_count(device)) // items)
     return max(1, min(wanted, pages // 2, 32))

@@ -16,30 +16,34 @@ def library():
     global _library
     if _library is None:
         lib = load_library("routed")
-        lib.kidi_route_choose.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.kidi_route.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p]
         lib.kidi_expert_slots.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.kidi_gather_slots.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                           c_void_p]
         lib.kidi_combine_slots.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                            c_void_p]
-        for name in ("kidi_route_choose", "kidi_expert_slots", "kidi_gather_slots", "kidi_combine_slots"):
+        for name in ("kidi_route", "kidi_expert_slots", "kidi_gather_slots", "kidi_combine_slots"):
             getattr(lib, name).restype = c_int
         _library = lib
     return _library
 
 
-def choose(logits: torch.Tensor, top: int, renormalise: bool):
-    """(chosen int32 [rows, top], weight float32 [rows, top]) from router logits float32 [rows, experts]:
-    sigmoid scores, the `top` largest (ties: the lower index), their scores as weights."""
-    ops._need_cuda(logits)
-    if logits.dtype != torch.float32 or logits.dim() != 2 or not logits.is_contiguous():
-        raise invalid_argument("the router's logits are a contiguous float32 matrix")
-    rows, experts = logits.shape
-    chosen = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
-    weight = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
-    _check(library().kidi_route_choose(logits.data_ptr(), chosen.data_ptr(), weight.data_ptr(), rows, experts, top,
-                                       1 if renormalise else 0, ops._stream()), "route_choose")
+def route(x: torch.Tensor, router: torch.Tensor, top: int, renormalise: bool):
+    """(chosen int32 [rows, top], weight float32 [rows, top]) for rows x [rows, hidden] and a router
+    [experts, hidden]: logits in 32-bit, sigmoid scores, the `top` largest (ties: the lower index), their scores as
+    weights."""
+    ops._need_cuda(x, router)
+    if x.dim() != 2 or not x.is_contiguous() or router.dim() != 2 or not router.is_contiguous() \
+            or router.shape[1] != x.shape[1]:
+        raise invalid_argument("the router takes contiguous rows and a contiguous [experts, hidden] matrix")
+    rows, hidden = x.shape
+    chosen = torch.empty((rows, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((rows, top), dtype=torch.float32, device=x.device)
+    _check(library().kidi_route(x.data_ptr(), dtype_code(x.dtype), router.data_ptr(), dtype_code(router.dtype),
+                                chosen.data_ptr(), weight.data_ptr(), rows, hidden, router.shape[0], top,
+                                1 if renormalise else 0, ops._stream()), "route")
     return chosen, weight
 
 

@@ -82,8 +82,7 @@ class RoutedExperts(Part):
     def forward(self, x, ctx) -> torch.Tensor:
         x = plain_rows(x)
         rows = x.shape[0]
-        logits = ops.gemm_simt(x, self.router, torch.float32)
-        chosen, weight = routed.choose(logits, self.top, self.renormalise)
+        chosen, weight = routed.route(x, self.router, self.top, self.renormalise)
         slots = rows * self.top
         if x.dtype == torch.float32 or self.gate_up.dtype == torch.float32 or ctx.plan.is_decode \
                 or slots <= SLOT_PATH_MAX:
