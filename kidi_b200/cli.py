@@ -42,7 +42,7 @@ class _Parser(argparse.ArgumentParser):
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = _Parser(prog="kidi_b200", description="Generation on one B200, in the manner of kidi (Qwen3 and Sanozen folders).")
+    parser = _Parser(prog="kidi_b200", description="Generation on one B200, in the manner of kidi (Qwen3, Sanozen and Gakenex folders).")
     commands = parser.add_subparsers(dest="command", metavar="COMMAND", parser_class=_Parser)
     commands.required = True
 

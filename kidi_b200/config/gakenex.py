@@ -6,7 +6,7 @@
                                                      | {kind: "moe", expert: {ff}, router: {experts, top}}}, ...]
 
 A layer's mixer: heads, kv_heads, dim (the width of a query or key map), vdim, conv (taps of the short
-convolution; absent or 1: none), diff, scale, mask: {size, keep_first} (absent: every earlier token is
+convolution; absent or 0: none), diff, scale, mask: {size, keep_first} (absent: every earlier token is
 visible; keep_first absent: 0). `logit_softcap` absent or 0: the logits are not bounded. A missing or
 ill-typed key is INVALID_MANIFEST naming the key.
 """
@@ -52,7 +52,9 @@ class GakenexLayer:
 
     def to_dict(self) -> dict:
         mixer: dict = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
-                       "conv": self.conv, "diff": self.diff, "scale": self.scale}
+                       "diff": self.diff, "scale": self.scale}
+        if self.conv:
+            mixer["conv"] = self.conv
         if self.window is not None:
             mixer["mask"] = {"size": self.window, "keep_first": self.keep_first}
         return {"type": self.type, "mixer": mixer, "mlp": self.mlp.to_dict() if self.mlp is not None else None}
@@ -111,7 +113,7 @@ class GakenexConfig:
                     raise unsupported(f"layers[{index}]: feed-forward kind '{mlp_kind}' is not supported")
             layers.append(GakenexLayer(
                 type=kind, heads=mixer.integer("heads"), kv_heads=mixer.integer("kv_heads"), dim=mixer.integer("dim"),
-                vdim=mixer.integer("vdim"), conv=mixer.integer("conv", 1), diff=mixer.number("diff"),
+                vdim=mixer.integer("vdim"), conv=mixer.integer("conv", 0), diff=mixer.number("diff"),
                 scale=mixer.number("scale"), window=window, keep_first=keep_first, mlp=feed_forward))
         eos = reader.raw("eos_token_id")
         if eos is None:
@@ -137,7 +139,7 @@ class GakenexConfig:
             raise invalid_manifest("invalid Gakenex configuration: logit_softcap cannot be negative")
         for index, layer in enumerate(self.layers):
             where = f"layers[{index}]"
-            if min(layer.heads, layer.kv_heads, layer.dim, layer.vdim, layer.conv) <= 0:
+            if min(layer.heads, layer.kv_heads, layer.dim, layer.vdim) <= 0 or layer.conv < 0:
                 raise invalid_manifest(f"{where}: every size must be positive")
             if layer.heads % layer.kv_heads:
                 raise invalid_manifest(f"{where}: heads must be a multiple of kv_heads")
@@ -145,8 +147,6 @@ class GakenexConfig:
                 raise invalid_manifest(f"{where}: mask.size must be positive")
             if layer.keep_first < 0:
                 raise invalid_manifest(f"{where}: mask.keep_first cannot be negative")
-            if not layer.scale > 0:
-                raise invalid_manifest(f"{where}: scale must be positive")
             mlp = layer.mlp
             if mlp is None:
                 continue

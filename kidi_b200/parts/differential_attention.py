@@ -4,7 +4,7 @@ With h the mixer's input, H query heads, G key/value heads (query head i reads k
 d the width of a map and e the width of a value head:
 
     q = W_q h  [H, 2, d],   k = W_k h  [G, 2, d],   v = W_v h  [G, e]         (no biases)
-    q, k, v <- a short causal convolution over time on every channel (`conv` taps; none: 1)
+    q, k, v <- a short causal convolution over time on every channel (`conv` taps; 0: none; 1: a weight a channel)
     q, k    <- per head and map: divided by the root mean square over d, times a weight of d entries
     a_m     = softmax over the visible keys of (q_m . k_m) * scale, times v            m = 1, 2
     o       = a_1 - lambda * a_2,   lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff   (one number a layer)
@@ -47,7 +47,7 @@ class DifferentialAttention(Part):
         self.kv_heads = int(spec.param("num_kv_heads"))
         self.dim = int(spec.param("dim"))
         self.vdim = int(spec.param("vdim"))
-        self.taps = int(spec.param("conv", 1) or 1)
+        self.taps = int(spec.param("conv", 0) or 0)
         self.diff = float(spec.param("diff", 0.0))
         self.eps = float(spec.param("eps"))
         scale = spec.param("scale", None)
@@ -58,8 +58,8 @@ class DifferentialAttention(Part):
             raise invalid_argument("invalid differential attention dimensions")
         if self.dim > 256 or self.vdim > 256:
             raise unsupported("differential attention takes maps and value heads of at most 256 entries")
-        if not 1 <= self.taps <= differential.MAX_TAPS:
-            raise unsupported(f"the short convolution takes 1 to {differential.MAX_TAPS} taps")
+        if not 0 <= self.taps <= differential.MAX_TAPS:
+            raise unsupported(f"the short convolution takes up to {differential.MAX_TAPS} taps")
         if self.window is not None and int(self.window) <= 0:
             raise invalid_argument("an attention window must be positive")
         if self.keep_first < 0:
@@ -87,7 +87,7 @@ class DifferentialAttention(Part):
             ParamSpec(n["k_norm"], (self.dim,), init=("one_plus_normal", 0.1)),
         ]
         specs += [ParamSpec(n[key], (self.dim,), init=("normal", 0.1)) for key in ("lq1", "lk1", "lq2", "lk2")]
-        if self.taps > 1:
+        if self.taps >= 1:
             specs.append(ParamSpec("qkv.conv", (self.channels, self.taps), init=("normal", 0.5), sources=(
                 (n["q_conv"], (self.q_width, self.taps)), (n["k_conv"], (self.k_width, self.taps)),
                 (n["v_conv"], (self.v_width, self.taps)))))
@@ -100,7 +100,7 @@ class DifferentialAttention(Part):
         # The small vectors are kept in 32-bit: norms, the convolution's sums and lambda are 32-bit arithmetic.
         self.q_norm = tensors[n["q_norm"]].float().contiguous()
         self.k_norm = tensors[n["k_norm"]].float().contiguous()
-        self.conv = tensors["qkv.conv"].float().contiguous() if self.taps > 1 else None
+        self.conv = tensors["qkv.conv"].float().contiguous() if self.taps >= 1 else None
         lq1, lk1, lq2, lk2 = (tensors[n[key]].float() for key in ("lq1", "lk1", "lq2", "lk2"))
         self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + self.diff)
 

@@ -43,7 +43,7 @@ class RMSNorm(Part):
     def prepared_weight(self) -> Optional[torch.Tensor]:
         """The weight vector a product needs to prepare rows for this norm (`ResidualSink`), or
         None when this norm does not take prepared rows."""
-        return self.weight if self.env.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 else None
+        return self.weight if self.env.dtype == torch.bfloat16 and not self.offset else None
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False,
                 out_dtype: Optional[torch.dtype] = None):

@@ -10,7 +10,9 @@ import torch
 
 
 def attention(heads, kv_heads, dim, vdim, conv, diff, scale, window=None, keep_first=0, mlp=None):
-    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "diff": diff, "scale": scale}
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": diff, "scale": scale}
+    if conv:
+        mixer["conv"] = conv
     if window is not None:
         mixer["mask"] = {"size": window, "keep_first": keep_first}
     return {"type": "attention", "mixer": mixer, "mlp": mlp}
@@ -36,7 +38,7 @@ def model(vocab, width, positions, eps, softcap, layers):
 SMALL_A = model(97, 64, 512, 1e-5, 20.0, [
     attention(2, 1, 16, 32, 4, 0.5, 0.3, window=40, keep_first=3, mlp=dense(96, 1.5)),
     attention(4, 4, 8, 8, 2, 0.3, 0.4, mlp=routed(6, 2, 24)),
-    attention(3, 1, 24, 16, 1, 0.7, 0.25, window=70, keep_first=0),
+    attention(3, 1, 24, 16, 0, 0.7, 0.25, window=70, keep_first=0),
 ])
 
 # a routed layer first; widths that are no multiples of 16; a window shorter than a page with kept tokens, and one
@@ -44,7 +46,7 @@ SMALL_A = model(97, 64, 512, 1e-5, 20.0, [
 SMALL_B = model(131, 72, 700, 3e-6, 0.0, [
     attention(6, 2, 12, 20, 3, 0.4, 0.3, window=17, keep_first=5, mlp=routed(5, 1, 20)),
     attention(2, 2, 16, 16, 2, 0.2, 0.35, window=200, keep_first=70, mlp=dense(100, 3.0)),
-    attention(1, 1, 40, 24, 4, 0.6, 0.2, window=64, keep_first=1, mlp=routed(3, 3, 16)),
+    attention(1, 1, 40, 24, 1, 0.6, 0.2, window=64, keep_first=1, mlp=routed(3, 3, 16)),     # one tap: a weight a channel
     attention(5, 1, 8, 12, 3, 0.8, 0.5, mlp=dense(64, 0.7)),
 ])
 
@@ -75,11 +77,11 @@ def tensors(config, seed, logit_scale=5.0, sharp=1.0):
            "embed.norm": normal(width, std=0.2), "final.norm": normal(width, std=0.1 * logit_scale, mean=logit_scale - 1)}
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        heads, groups, dim, vdim, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+        heads, groups, dim, vdim, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv", 0)
         out[p + "norm1"] = normal(width, std=0.2)
         for name, rows in (("q", heads * 2 * dim), ("k", groups * 2 * dim), ("v", groups * vdim)):
             out[p + "mix." + name] = matrix(rows, width, 1.5)
-            if taps > 1:
+            if taps >= 1:
                 out[p + "mix." + name + ".conv"] = normal(rows, taps, std=0.5, mean=0.3)
         out[p + "mix.q.norm"] = normal(dim, std=0.2 * sharp, mean=1.0 * sharp)
         out[p + "mix.k.norm"] = normal(dim, std=0.2, mean=1.0)

@@ -78,7 +78,7 @@ def test_a_random_model_folder_through_the_command_line(tmp_path, capsys):
                            "--seed", "3"]) == 0, capsys.readouterr().err
     held = Checkpoint(str(tmp_path / "model"))
     assert held.shape("l1.mlp.e5.down") == (64, 24) and held.shape("l0.mix.q.conv") == (64, 4)
-    assert "l2.mix.q.conv" not in held and "head" not in held
+    assert "l2.mix.q.conv" not in held and "head" not in held        # a layer without convolution
     held.close()
     assert kidi_b200.main(["inspect", "-m", str(tmp_path / "model")]) == 0
     assert "Gakenex" in capsys.readouterr().out
