@@ -75,10 +75,30 @@ struct DiffPrepareArgs {
     int move_state;        // 1: one token a sequence, the state is moved on here
 };
 
+// V consecutive elements of a row, as floats (V = 2: a bfloat16 pair in one 4-byte access).
+template <typename T, int V> __device__ __forceinline__ void load_elements(const T* p, float (&out)[V]) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) out[v] = to_float(p[v]);
+}
+template <> __device__ __forceinline__ void load_elements<bf16, 2>(const bf16* p, float (&out)[2]) {
+    const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    out[0] = pair.x;
+    out[1] = pair.y;
+}
+template <typename T, int V> __device__ __forceinline__ void store_elements(T* p, const float (&in)[V]) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) p[v] = from_float<T>(in[v]);
+}
+template <> __device__ __forceinline__ void store_elements<bf16, 2>(bf16* p, const float (&in)[2]) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(in[0], in[1]);
+}
+
 // One warp per (row, unit): units are the 2 * heads query maps, the 2 * kv_heads key maps and the
-// kv_heads value heads, in the projection's order.
-template <typename T, typename TW>
+// kv_heads value heads, in the projection's order. A lane takes V consecutive channels at a time
+// (V = 2 for bfloat16 rows of even widths: 128 bytes a warp and access).
+template <typename T, typename TW, int V>
 __global__ void __launch_bounds__(128) diff_prepare_kernel(DiffPrepareArgs a) {
+    constexpr int ROUNDS = 8 / V;
     const DiffGeometry& g = a.geometry;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_units = 2 * g.heads, k_units = 2 * g.kv_heads, units = q_units + k_units + g.kv_heads;
@@ -98,31 +118,39 @@ __global__ void __launch_bounds__(128) diff_prepare_kernel(DiffPrepareArgs a) {
     const int taps = conv ? a.taps : 1;
     T* state = (T*)a.state + (long long)slot * (taps - 1) * channels;
 
-    float values[8];
+    float values[ROUNDS][V];
     float square = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int c = lane + 32 * i;
-        float y = 0.f;
+    for (int i = 0; i < ROUNDS; ++i) {
+        const int c = (lane + 32 * i) * V;
+        float y[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] = 0.f;
         if (c < width) {
             const int channel = base + c;
             if (!conv) {
-                y = to_float(proj[(long long)row * a.ld + channel]);
+                load_elements<T, V>(proj + (long long)row * a.ld + channel, y);
             } else {
                 for (int j = 0; j < taps; ++j) {
                     const int t = position - (taps - 1) + j;
-                    float u = 0.f;
-                    if (t >= start) u = to_float(proj[(long long)(row0 + t - start) * a.ld + channel]);
-                    else if (t >= 0) u = to_float(state[(long long)(t - (start - (taps - 1))) * channels + channel]);
-                    y = fmaf(to_float(conv[(long long)channel * taps + j]), u, y);
-                    // One token a sequence: this lane alone reads and writes its channel's state, and row j - 1
+                    float u[V];
+#pragma unroll
+                    for (int v = 0; v < V; ++v) u[v] = 0.f;
+                    if (t >= start) load_elements<T, V>(proj + (long long)(row0 + t - start) * a.ld + channel, u);
+                    else if (t >= 0) load_elements<T, V>(state + (long long)(t - (start - (taps - 1))) * channels + channel, u);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) y[v] = fmaf(to_float(conv[(long long)(channel + v) * taps + j]), u[v], y[v]);
+                    // One token a sequence: this lane alone reads and writes its channels' state, and row j - 1
                     // was read an iteration ago.
-                    if (a.move_state && j > 0) state[(long long)(j - 1) * channels + channel] = from_float<T>(u);
+                    if (a.move_state && j > 0) store_elements<T, V>(state + (long long)(j - 1) * channels + channel, u);
                 }
             }
         }
-        values[i] = y;
-        square = fmaf(y, y, square);
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            values[i][v] = y[v];
+            square = fmaf(y[v], y[v], square);
+        }
     }
     if (unit < q_units + k_units) {
         const TW* weight = (const TW*)(unit < q_units ? a.q_norm : a.k_norm);
@@ -135,16 +163,21 @@ __global__ void __launch_bounds__(128) diff_prepare_kernel(DiffPrepareArgs a) {
             out = (T*)a.k_cache + diff_page_row(g, slot, position, k_unit >> 1) * (2 * g.dim) + (k_unit & 1) * g.dim;
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = lane + 32 * i;
-            if (c < width) out[c] = from_float<T>(values[i] * inv * to_float(weight[c]));
+        for (int i = 0; i < ROUNDS; ++i) {
+            const int c = (lane + 32 * i) * V;
+            if (c < width) {
+                float normed[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) normed[v] = values[i][v] * inv * to_float(weight[c + v]);
+                store_elements<T, V>(out + c, normed);
+            }
         }
     } else {
         T* out = (T*)a.v_cache + diff_page_row(g, slot, position, unit - q_units - k_units) * g.vdim;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = lane + 32 * i;
-            if (c < width) out[c] = from_float<T>(values[i]);
+        for (int i = 0; i < ROUNDS; ++i) {
+            const int c = (lane + 32 * i) * V;
+            if (c < width) store_elements<T, V>(out + c, values[i]);
         }
     }
 }
@@ -181,18 +214,24 @@ KIDI_API int kidi_diff_prepare(const DiffPrepareArgs* args, int dtype, int weigh
     const long long items = (long long)a.rows * (2 * g.heads + 3 * g.kv_heads);
     const unsigned blocks = (unsigned)((items + 3) / 4);
     int status;
-#define KIDI_CASE(D, T, W, TW)                                                                     \
-    if (dtype == D && weight_dtype == W) {                                                         \
-        status = kidi_launch(diff_prepare_kernel<T, TW>, blocks, 128, 0, stream, a);              \
+    // bfloat16 rows of even widths: a lane takes pairs
+    const bool pairs = dtype == KIDI_BF16 && !(g.dim & 1) && !(g.vdim & 1) && !(a.ld & 1) && !((uintptr_t)a.proj & 3) &&
+                       !((uintptr_t)a.state & 3) && !((uintptr_t)a.q_out & 3) && !((uintptr_t)a.k_cache & 3) &&
+                       !((uintptr_t)a.v_cache & 3);
+#define KIDI_CASE(D, T, W, TW, V)                                                                  \
+    if (dtype == D && weight_dtype == W && pairs == (V == 2)) {                                    \
+        status = kidi_launch(diff_prepare_kernel<T, TW, V>, blocks, 128, 0, stream, a);           \
         if (status || !a.conv || a.taps < 2 || a.move_state) return status;                       \
         const int channels = 2 * (g.heads + g.kv_heads) * g.dim + g.kv_heads * g.vdim;            \
         const long long total = (long long)a.seqs * channels;                                     \
         return kidi_launch(diff_state_kernel<T>, (unsigned)((total + 255) / 256), 256, 0, stream, a, channels); \
     }
-    KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
-    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
-    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
-    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
+    KIDI_CASE(KIDI_F32, float, KIDI_F32, float, 1)
+    KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16, 1)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, 1)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, 1)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float, 2)
+    KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16, 2)
 #undef KIDI_CASE
     return KIDI_REFUSED_DTYPE;
 }

@@ -262,6 +262,57 @@ __global__ void combine_slots_kernel(const T* __restrict__ y, const int* __restr
     out[index] = from_float<T>(sum);
 }
 
+// The same two for bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) a thread.
+__global__ void gather_slots_bf16x8_kernel(const bf16* __restrict__ x, const int* __restrict__ order,
+                                           const float* __restrict__ weight, bf16* __restrict__ gathered, long long groups,
+                                           int top, int hidden, int weight_on_input) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= groups) return;
+    const int per_row = hidden >> 3;
+    const long long i = index / per_row;
+    const int c = (int)(index - i * per_row) << 3;
+    const int slot = order[i];
+    uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)(slot / top) * hidden + c);
+    if (weight_on_input) {
+        const float w = weight[slot];
+        __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 v = __bfloat1622float2(pairs[k]);
+            pairs[k] = __floats2bfloat162_rn(v.x * w, v.y * w);
+        }
+    }
+    *reinterpret_cast<uint4*>(gathered + i * hidden + c) = raw;
+}
+
+__global__ void combine_slots_bf16x8_kernel(const bf16* __restrict__ y, const int* __restrict__ place,
+                                            const float* __restrict__ weight, bf16* __restrict__ out, long long groups,
+                                            int top, int hidden, int weight_on_input) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= groups) return;
+    const int per_row = hidden >> 3;
+    const long long row = index / per_row;
+    const int c = (int)(index - row * per_row) << 3;
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+        const long long slot = row * top + k;
+        const uint4 raw = *reinterpret_cast<const uint4*>(y + (long long)place[slot] * hidden + c);
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float w = weight_on_input ? 1.f : weight[slot];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(pairs[j]);
+            sum[2 * j] += weight_on_input ? v.x : v.x * w;
+            sum[2 * j + 1] += weight_on_input ? v.y : v.y * w;
+        }
+    }
+    uint4 result;
+    __nv_bfloat162* packed = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed[j] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + row * hidden + c) = result;
+}
+
 KIDI_API int kidi_gather_slots(const void* x, int dtype, const int* order, const float* weight, void* gathered, int slots,
                                int top, int hidden, int weight_on_input, cudaStream_t stream) {
     const long long total = (long long)slots * hidden;
@@ -269,6 +320,9 @@ KIDI_API int kidi_gather_slots(const void* x, int dtype, const int* order, const
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == KIDI_F32) return kidi_launch(gather_slots_kernel<float>, blocks, 256, 0, stream, (const float*)x, order,
                                               weight, (float*)gathered, total, top, hidden, weight_on_input);
+    if (dtype == KIDI_BF16 && !(hidden & 7) && !((uintptr_t)x & 15) && !((uintptr_t)gathered & 15))
+        return kidi_launch(gather_slots_bf16x8_kernel, (unsigned)(((total >> 3) + 255) / 256), 256, 0, stream,
+                           (const bf16*)x, order, weight, (bf16*)gathered, total >> 3, top, hidden, weight_on_input);
     if (dtype == KIDI_BF16) return kidi_launch(gather_slots_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)x, order,
                                                weight, (bf16*)gathered, total, top, hidden, weight_on_input);
     return KIDI_REFUSED_DTYPE;
@@ -281,6 +335,9 @@ KIDI_API int kidi_combine_slots(const void* y, int dtype, const int* place, cons
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == KIDI_F32) return kidi_launch(combine_slots_kernel<float>, blocks, 256, 0, stream, (const float*)y, place,
                                               weight, (float*)out, total, top, hidden, weight_on_input);
+    if (dtype == KIDI_BF16 && !(hidden & 7) && !((uintptr_t)y & 15) && !((uintptr_t)out & 15))
+        return kidi_launch(combine_slots_bf16x8_kernel, (unsigned)(((total >> 3) + 255) / 256), 256, 0, stream,
+                           (const bf16*)y, place, weight, (bf16*)out, total >> 3, top, hidden, weight_on_input);
     if (dtype == KIDI_BF16) return kidi_launch(combine_slots_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)y, place,
                                                weight, (bf16*)out, total, top, hidden, weight_on_input);
     return KIDI_REFUSED_DTYPE;

@@ -67,11 +67,12 @@ def test_the_small_kernels(dtype):
     """The bounded gate, the bounded logits and the rows of a position table, each against its formula."""
     from kidi_b200.kernels import ops
     generator = torch.Generator().manual_seed(3)
-    both = (torch.randn(7, 2 * 37, generator=generator) * 3).to(dtype).cuda()
-    found = ops.bounded_gate(both, 2.5, 1.702, 1.0).double().cpu()
-    g, u = both.double().cpu()[:, :37].clamp(max=2.5), both.double().cpu()[:, 37:].clamp(-2.5, 2.5)
-    assert torch.allclose(found, g * torch.sigmoid(1.702 * g) * (u + 1.0), atol=1e-6 if dtype == torch.float32 else 6e-2)
-    assert float((g.max() - 2.5).abs()) < 1e-9 and float(u.min() + 2.5) < 1e-9      # the bounds are reached
+    for inter in (37, 40):              # one by one, and in 16-byte pieces
+        both = (torch.randn(7, 2 * inter, generator=generator) * 3).to(dtype).cuda()
+        found = ops.bounded_gate(both, 2.5, 1.702, 1.0).double().cpu()
+        g, u = both.double().cpu()[:, :inter].clamp(max=2.5), both.double().cpu()[:, inter:].clamp(-2.5, 2.5)
+        assert torch.allclose(found, g * torch.sigmoid(1.702 * g) * (u + 1.0), atol=1e-6 if dtype == torch.float32 else 6e-2)
+        assert float((g.max() - 2.5).abs()) < 1e-9 and float(u.min() + 2.5) < 1e-9      # the bounds are reached
     logits = (torch.randn(5, 33, generator=generator) * 20).cuda()
     want = 9.0 * torch.tanh(logits.double().cpu() / 9.0)
     assert torch.allclose(ops.tanh_cap(logits.clone(), 9.0).double().cpu(), want, atol=1e-5)
