@@ -156,14 +156,14 @@ def attention(ctx, q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
 
 def tensor_splits(seqs: int, kv_heads: int, reach: int, device: torch.device) -> int:
     """How many blocks share the keys of a (sequence, key/value head) when every sequence brings one token:
-    as many as still run in one round of blocks (two a multiprocessor, by their registers), at most one per
-    two pages of 64 keys. Measured on a B200 at 8 sequences x 8 key/value heads x 1,026 tokens: 3 or 4 shares
-    28 us a layer, 6 shares (two rounds) 38 us."""
+    as many as fill three quarters of one round of blocks (two a multiprocessor, by their registers), at most one
+    per two pages of 64 keys. Measured on a B200 at 8 sequences x 8 key/value heads x 1,026 tokens: 3 shares 28 us
+    a layer, 4 shares 32 us, 6 shares (two rounds) 38 us."""
     from .attention import sm_count
     forced = int(os.environ.get("KIDI_B200_DECODE_SPLITS", "0"))
     pages = max(1, -(-reach // 64))
     if forced:
         return max(1, min(pages, forced))
     items = max(1, seqs * kv_heads)
-    wanted = max(1, (2 * sm_count(device)) // items)
+    wanted = max(1, (3 * sm_count(device)) // (2 * items))
     return max(1, min(wanted, pages // 2, 32))

@@ -172,6 +172,34 @@ def test_window_edges_and_kept_tokens(dtype, dim, vdim, record_property):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,keep_first,sharp", [(20, 4, 1.0), (None, 0, 3.0)])
+def test_far_keys_reach_the_last_rows(dtype, window, keep_first, sharp, record_property):
+    """449 tokens, seven pages of the cache: with a window of 20 the last rows still see the four kept tokens, and
+    without a window (sharp scores) every token. Another token at position 2 moves the plain model's last rows
+    clearly, so a kept or far key that is lost, or read from a wrong page, shows: whole, and with the last eight
+    tokens decoded one by one."""
+    config = one_layer(window, keep_first, heads=4, kv_heads=2, dim=16, vdim=32, conv=2)
+    tensors = gakenex_configs.tensors(config, 31, sharp=sharp)
+    tokens = prompt(config, 449, 7)
+    want = plain(config, tensors, tokens)
+    other = plain(config, tensors, tokens[:2] + [(tokens[2] + 1) % config["vocab"]] + tokens[3:])
+    moved = float((other[-8:] - want[-8:]).abs().max()) / float(want.abs().max())
+    record_property("what the far token moves", moved)
+    assert moved > 20 * LARGEST["float32"]
+    engine, _, _ = make(None, dtype, config=config, tensors=tensors)
+    slot = engine.acquire()
+    whole = run(engine, slot, tokens)
+    engine.release(slot)
+    slot = engine.acquire()
+    run(engine, slot, tokens[:-8], want=[])
+    decoded = torch.cat([run(engine, slot, [token]) for token in tokens[-8:]])
+    engine.release(slot)
+    for got, what in ((whole[-8:], "whole"), (decoded, "decoded")):
+        close(got, want[-8:], dtype, record_property, what)
+        assert float((got - want[-8:]).pow(2).mean().sqrt()) < 0.5 * float((got - other[-8:]).pow(2).mean().sqrt()), what
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_first_tokens_and_the_convolution_state(dtype, record_property):
     """Four taps: a sequence's first rows see zeros before its start, and a sequence that comes in portions of 1,
     1, 2, 1 and 3 tokens, shorter than the taps, carries its last three projected rows from step to step; a slot
