@@ -311,13 +311,13 @@ def sanozen_shape(width: int, layers: int = 4) -> dict:
 
 def gakenex_shape(width: int, layers: int = 4) -> dict:
     """A Gakenex stack at the layer sizes of a model of `width`: heads with two maps of 64 and values of 128, a
-    key/value head for four heads, four convolution taps, a window of 4,096 with four kept tokens; dense
+    key/value head for four heads, four convolution taps, a window of 4,096 with eight kept tokens; dense
     feed-forwards of the Qwen3 layers' size in turn with routed ones (16 experts, two a token, each half that
     size, so that a token uses as many weights)."""
     heads = width // 128
     inter = (8 * width // 3 + 127) // 128 * 128
-    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6,
-             "scale": 64 ** -0.5, "mask": {"size": 4096, "keep_first": 4}}
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "conv": 4, "diff": 0.5,
+             "scale": 64 ** -0.5, "mask": {"size": 4096, "keep_first": 8}}
     stack = []
     for index in range(layers):
         mlp = {"kind": "dense", "ff": inter, "limit": 7.0} if index % 2 == 0 else \
