@@ -385,9 +385,12 @@ KIDI_API int kidi_diff_attention_generic(const DiffAttentionArgs* args, int dtyp
 // ---------------------------------------------------------------------------
 // The tensor-core kernels (bfloat16), compiled for one pair of widths.
 //
-// A block of four warps takes rows of one sequence that share a key/value head: in a prompt, 64 rows
-// = 64 / (heads per key/value head) consecutive tokens times those heads, a warp 16 rows and all 64
-// keys of a tile; with one token a sequence, the 16 (or fewer) heads of the token, each warp a
+// A block takes rows of one sequence that share a key/value head. In a prompt: 64 rows = 64 / (heads per
+// key/value head) consecutive tokens times those heads, and eight warps: a warp takes 16 rows, all 64
+// keys of a tile and ONE of the two maps (so that a map's weighted sum of 16 rows by vdim columns is what
+// a warp holds, and twice as many warps fit a multiprocessor as with both maps to a warp); the warps of
+// the second map hand their result to those of the first through shared memory at the end. With one
+// token a sequence: four warps, the 16 (or fewer) heads of the token, each warp both maps and a
 // quarter of a tile's keys, merged through shared memory at the end. A tile is a 64-token page of
 // the cache (keys of both maps, values), copied with cp.async into one of two buffers while the
 // other is used. The tiles a block visits are the pages of its window and, before them, the pages
@@ -447,7 +450,9 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // ROW_WARPS 4: prompts (64 rows a block); 1: one token a sequence (16 rows, the warps share a tile's keys).
 template <int ROW_WARPS>
-__global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentionArgs a) {
+__global__ void __launch_bounds__(ROW_WARPS == 4 ? 256 : 128, 2) diff_attention_tensor_kernel(DiffAttentionArgs a) {
+    constexpr int MAPS = ROW_WARPS == 4 ? 1 : 2;          // maps a warp takes
+    constexpr int THREADS = ROW_WARPS == 4 ? 256 : 128;
     constexpr int KEY_WARPS = 4 / ROW_WARPS;
     constexpr int ROWS = 16 * ROW_WARPS;
     constexpr int KEYS_W = TILE / KEY_WARPS;
@@ -470,7 +475,7 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
     bf16* out = (bf16*)a.out;
     if (a.tables.row_seq[row0] < 0) {          // a padding sequence of a captured step: zeros, nothing read
         if (split == 0 && a.splits == 1)
-            for (int i = tid; i < live_rows * VDIM; i += 128) {
+            for (int i = tid; i < live_rows * VDIM; i += THREADS) {
                 const int r = i / VDIM, c = i - r * VDIM;
                 out[((long long)(row0 + t0 + r / group) * g.heads + kv_head * group + r % group) * VDIM + c] =
                     __float2bfloat16_rn(0.f);
@@ -496,39 +501,43 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
         const bf16* values = v_cache + at * VDIM;
         bf16* k_to = k_s + buffer * TILE * KS;
         bf16* v_to = v_s + buffer * TILE * VS;
-        for (int i = tid; i < TILE * (2 * DIM / 8); i += 128) {
+        for (int i = tid; i < TILE * (2 * DIM / 8); i += THREADS) {
             const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
             copy16(k_to + r * KS + piece * 8, keys + r * (2 * DIM) + piece * 8);
         }
-        for (int i = tid; i < TILE * (VDIM / 8); i += 128) {
+        for (int i = tid; i < TILE * (VDIM / 8); i += THREADS) {
             const int r = i / (VDIM / 8), piece = i - r * (VDIM / 8);
             copy16(v_to + r * VS + piece * 8, values + r * VDIM + piece * 8);
         }
         asm volatile("cp.async.commit_group;");
     };
 
-    const int row_warp = warp / KEY_WARPS, key0 = (warp % KEY_WARPS) * KEYS_W;
+    // prompts: warps 0..3 take the first map of rows 16 w.., warps 4..7 the second; one token: each warp both maps
+    const int own_map = MAPS == 1 ? warp >> 2 : 0;
+    const int row_warp = MAPS == 1 ? warp & 3 : 0, key0 = MAPS == 1 ? 0 : warp * KEYS_W;
     const int row_a = row_warp * 16 + (lane >> 2), row_b = row_a + 8;
     // A row's position; -1 for rows beyond the block's live rows: they see nothing.
     const int pos_a = row_a < live_rows ? start + t0 + row_a / group : -1;
     const int pos_b = row_b < live_rows ? start + t0 + row_b / group : -1;
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
-    float o[2][NV][4];
-    float top_a[2] = {-INFINITY, -INFINITY}, top_b[2] = {-INFINITY, -INFINITY};
-    float sum_a[2] = {0.f, 0.f}, sum_b[2] = {0.f, 0.f};
+    float o[MAPS][NV][4];
+    float top_a[MAPS], top_b[MAPS], sum_a[MAPS], sum_b[MAPS];
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int m = 0; m < MAPS; ++m) {
+        top_a[m] = top_b[m] = -INFINITY;
+        sum_a[m] = sum_b[m] = 0.f;
 #pragma unroll
         for (int n = 0; n < NV; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
+    }
 
     if (first_tile < end_tile) load_tile(first_tile, 0);
     // The block's query rows (while the first tile is on its way): row r is token t0 + r / group, head
     // kv_head * group + r % group.
     const bf16* q = (const bf16*)a.q;
-    for (int i = tid; i < ROWS * (2 * DIM / 8); i += 128) {
+    for (int i = tid; i < ROWS * (2 * DIM / 8); i += THREADS) {
         const int r = i / (2 * DIM / 8), piece = i - r * (2 * DIM / 8);
         uint4 value = make_uint4(0u, 0u, 0u, 0u);
         if (r < live_rows)
@@ -552,18 +561,19 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
         const bool whole = tile_key + TILE - 1 <= p_low &&
                            (a.window <= 0 || p_high - tile_key < a.window || tile_key + TILE - 1 < a.keep_first);
 #pragma unroll
-        for (int m = 0; m < 2; ++m) {
+        for (int m = 0; m < MAPS; ++m) {
+            const int map = MAPS == 1 ? own_map : m;          // which of the two maps of queries and keys
             float s[NT][4];
 #pragma unroll
             for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < DIM / 16; ++ks) {
                 uint32_t qa[4];
-                ldmatrix_x4(qa, q_s + (row_warp * 16 + (lane & 15)) * KS + m * DIM + ks * 16 + (lane >> 4) * 8);
+                ldmatrix_x4(qa, q_s + (row_warp * 16 + (lane & 15)) * KS + map * DIM + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
                 for (int n2 = 0; n2 < NT / 2; ++n2) {
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, k_tile + (key0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + m * DIM + ks * 16 +
+                    ldmatrix_x4(kb, k_tile + (key0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + map * DIM + ks * 16 +
                                         ((lane >> 3) & 1) * 8);
                     mma_bf16(s[2 * n2], qa, kb[0], kb[1]);
                     mma_bf16(s[2 * n2 + 1], qa, kb[2], kb[3]);
@@ -628,14 +638,14 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
         __syncthreads();
     }
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    for (int m = 0; m < MAPS; ++m) {
         sum_a[m] = quad_sum(sum_a[m]);
         sum_b[m] = quad_sum(sum_b[m]);
         top_a[m] *= scale_log2;           // from here on the largest scores are exponents of two (-inf stays)
         top_b[m] *= scale_log2;
     }
 
-    if (KEY_WARPS > 1) {
+    if constexpr (KEY_WARPS > 1) {
         // The four warps hold the same 16 rows over different keys: they meet in shared memory, behind the
         // query rows, and the first warp adds them up.
         float* stage = reinterpret_cast<float*>(shared_bytes + ((ROWS * KS * 2 + 15) & ~15));   // [4][2][16][STAGE]
@@ -693,12 +703,42 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
     // Each map's weighted sum divided by its softmax sum (a row without a key, which only a share of
     // the tiles can be, gives zeros and a zero sum).
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    for (int m = 0; m < MAPS; ++m) {
         const float inv_a = sum_a[m] > 0.f ? 1.0f / sum_a[m] : 0.f, inv_b = sum_b[m] > 0.f ? 1.0f / sum_b[m] : 0.f;
 #pragma unroll
         for (int n = 0; n < NV; ++n) {
             o[m][n][0] *= inv_a; o[m][n][1] *= inv_a;
             o[m][n][2] *= inv_b; o[m][n][3] *= inv_b;
+        }
+    }
+    // The second map's result, where the first map's is: in the same warp (one token a sequence), or handed over
+    // by the warp four further on through shared memory (prompts), behind the query rows.
+    float second[NV][4];
+    if constexpr (MAPS == 2) {
+#pragma unroll
+        for (int n = 0; n < NV; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) second[n][e] = o[1][n][e];
+    } else {
+        float* stage = reinterpret_cast<float*>(shared_bytes + ((ROWS * KS * 2 + 15) & ~15)) + row_warp * 16 * STAGE;
+        __syncthreads();
+        if (own_map == 1) {
+#pragma unroll
+            for (int n = 0; n < NV; ++n) {
+                const int c = n * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(stage + (lane >> 2) * STAGE + c) = make_float2(o[0][n][0], o[0][n][1]);
+                *reinterpret_cast<float2*>(stage + ((lane >> 2) + 8) * STAGE + c) = make_float2(o[0][n][2], o[0][n][3]);
+            }
+        }
+        __syncthreads();
+        if (own_map == 1) return;
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int c = n * 8 + (lane & 3) * 2;
+            const float2 upper = *reinterpret_cast<const float2*>(stage + (lane >> 2) * STAGE + c);
+            const float2 lower = *reinterpret_cast<const float2*>(stage + ((lane >> 2) + 8) * STAGE + c);
+            second[n][0] = upper.x; second[n][1] = upper.y;
+            second[n][2] = lower.x; second[n][3] = lower.y;
         }
     }
 #pragma unroll
@@ -707,27 +747,30 @@ __global__ void __launch_bounds__(128) diff_attention_tensor_kernel(DiffAttentio
         const bool live = r < live_rows;
         const long long row = row0 + t0 + (live ? r / group : 0);
         const int head = kv_head * group + (live ? r % group : 0);
-        if (a.splits > 1) {
-            if (live) {
-                float* to = a.partial + ((row * g.heads + head) * a.splits + split) * (2 * VDIM + 4);
+        if constexpr (MAPS == 2) {
+            if (a.splits > 1) {
+                if (live) {
+                    float* to = a.partial + ((row * g.heads + head) * a.splits + split) * (2 * VDIM + 4);
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
-#pragma unroll
-                    for (int n = 0; n < NV; ++n)
-                        *reinterpret_cast<float2*>(to + m * VDIM + n * 8 + (lane & 3) * 2) =
-                            make_float2(o[m][n][2 * half], o[m][n][2 * half + 1]);
-                if ((lane & 3) == 0) {
-                    to[2 * VDIM] = half ? top_b[0] : top_a[0]; to[2 * VDIM + 1] = half ? sum_b[0] : sum_a[0];
-                    to[2 * VDIM + 2] = half ? top_b[1] : top_a[1]; to[2 * VDIM + 3] = half ? sum_b[1] : sum_a[1];
+                    for (int n = 0; n < NV; ++n) {
+                        *reinterpret_cast<float2*>(to + n * 8 + (lane & 3) * 2) = make_float2(o[0][n][2 * half], o[0][n][2 * half + 1]);
+                        *reinterpret_cast<float2*>(to + VDIM + n * 8 + (lane & 3) * 2) =
+                            make_float2(second[n][2 * half], second[n][2 * half + 1]);
+                    }
+                    if ((lane & 3) == 0) {
+                        to[2 * VDIM] = half ? top_b[0] : top_a[0]; to[2 * VDIM + 1] = half ? sum_b[0] : sum_a[0];
+                        to[2 * VDIM + 2] = half ? top_b[MAPS - 1] : top_a[MAPS - 1];
+                        to[2 * VDIM + 3] = half ? sum_b[MAPS - 1] : sum_a[MAPS - 1];
+                    }
                 }
+                continue;
             }
-            continue;
         }
         float square = 0.f;
 #pragma unroll
         for (int n = 0; n < NV; ++n) {
-            const float x = o[0][n][2 * half] - a.lambda * o[1][n][2 * half];
-            const float y = o[0][n][2 * half + 1] - a.lambda * o[1][n][2 * half + 1];
+            const float x = o[0][n][2 * half] - a.lambda * second[n][2 * half];
+            const float y = o[0][n][2 * half + 1] - a.lambda * second[n][2 * half + 1];
             o[0][n][2 * half] = x;
             o[0][n][2 * half + 1] = y;
             square = fmaf(x, x, fmaf(y, y, square));
@@ -816,7 +859,8 @@ KIDI_API int kidi_diff_attention_tensor(const DiffAttentionArgs* args, cudaStrea
         const long long items = (long long)a.rows * g.heads;
         return kidi_launch(diff_combine_kernel, (unsigned)((items + 3) / 4), 128, 0, stream, a);
     }
-    const size_t shared = (size_t)64 * KS * sizeof(bf16) + tiles;
+    const size_t handed = (size_t)4 * 16 * STAGE * sizeof(float);          // the second map's results on their way
+    const size_t shared = (((size_t)64 * KS * sizeof(bf16) + 15) & ~(size_t)15) + (tiles > handed ? tiles : handed);
     static bool set = false;
     if (!set) {
         cudaError_t error = cudaFuncSetAttribute(diff_attention_tensor_kernel<4>,
@@ -825,7 +869,7 @@ KIDI_API int kidi_diff_attention_tensor(const DiffAttentionArgs* args, cudaStrea
         set = true;
     }
     const int tokens = 64 / group;
-    return kidi_launch(diff_attention_tensor_kernel<4>, dim3((a.max_new + tokens - 1) / tokens, a.seqs, g.kv_heads), 128,
+    return kidi_launch(diff_attention_tensor_kernel<4>, dim3((a.max_new + tokens - 1) / tokens, a.seqs, g.kv_heads), 256,
                        shared, stream, a);
 }
 #endif
