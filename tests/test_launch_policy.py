@@ -73,3 +73,21 @@ def test_which_product_a_shape_goes_to():
     assert tcgen05.fits_prompt(*operands(2048, 4096)) and tcgen05.fits_prompt(*operands(1024, 6144))
     assert not tcgen05.fits_prompt(*operands(1023, 4096)) and not tcgen05.fits_prompt(*operands(2048, 4096, width=4100))
     assert tcgen05.MIN_GATED_ROWS == skinny.MAX_ROWS + 1          # no batch size falls between the two kernels
+
+
+def test_shares_of_differential_decode_attention(monkeypatch):
+    """One token a sequence: a (sequence, key/value head)'s pages are dealt to as many blocks as fill three quarters
+    of one round of two blocks a multiprocessor, at most one per two pages; the kernels take bfloat16 widths that
+    are multiples of 16 up to 128."""
+    from kidi_b200.kernels import differential
+    assert differential.tensor_splits(8, 8, 1026, DEVICE) == 3            # 64 pairs on 222 places
+    assert differential.tensor_splits(1, 1, 64, DEVICE) == 1              # one page: nothing to share
+    assert differential.tensor_splits(1, 2, 8192, DEVICE) == 32           # never more than 32
+    assert differential.tensor_splits(1, 8, 300, DEVICE) == 2             # five pages: two shares
+    assert differential.tensor_splits(64, 8, 4096, DEVICE) == 1           # more pairs than places
+    monkeypatch.setenv("KIDI_B200_DECODE_SPLITS", "5")
+    assert differential.tensor_splits(64, 8, 4096, DEVICE) == 5 and differential.tensor_splits(1, 1, 100, DEVICE) == 2
+    monkeypatch.setattr(differential, "FORCE_GENERAL", False)
+    assert differential.tensor_fits(torch.bfloat16, 32, 80, 64) and differential.tensor_fits(torch.bfloat16, 128, 16, 64)
+    assert not differential.tensor_fits(torch.float32, 32, 80, 64) and not differential.tensor_fits(torch.bfloat16, 40, 80, 64)
+    assert not differential.tensor_fits(torch.bfloat16, 144, 80, 64) and not differential.tensor_fits(torch.bfloat16, 32, 80, 32)
