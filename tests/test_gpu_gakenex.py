@@ -418,3 +418,45 @@ def test_the_command_line_generates(tmp_path, capsys):
     for record in records:
         request = requests[int(record["id"])]
         assert teacher_forced(config, tensors, request, record["token_ids"], LARGEST["float32"]) == (0, 0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_trace_runner_replays_a_model_folder(tmp_path, dtype, record_property):
+    """bin/trace_run on a Gakenex folder: three unequal requests start together (one of a single token), are decoded
+    together until the shorter ones end, a step in which nothing is wanted, then a fourth request on what they gave
+    back. `--max-tokens` is the tokens they hold, with no allowance for partly filled pages."""
+    import os
+    import subprocess
+    import sys
+    from kidi_b200.weights.safetensors_io import write_safetensors
+    config = gakenex_configs.SMALL_B
+    tensors = gakenex_configs.tensors(config, 9)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(config))
+    write_safetensors(str(folder / "model.safetensors"), tensors, metadata={"format": "pt"})
+    a, b, c, d = (prompt(config, n, 60 + n) for n in (1, 75, 133, 90))
+    want = {name: plain(config, tensors, tokens) for name, tokens in (("a", a), ("b", b), ("c", c), ("d", d))}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a, "want": [0]}, {"id": "b", "tokens": b[:70], "want": [0, 69]},
+                                     {"id": "c", "tokens": c[:129], "want": [5, 128]}], "end": ["a"]}]
+    for index in range(5):
+        entries = [{"id": "b", "tokens": [b[70 + index]], "want": [0] if index != 2 else []}]
+        if index < 4:
+            entries.append({"id": "c", "tokens": [c[129 + index]], "want": [0] if index != 2 else []})
+        steps.append({"step": 1 + index, "entries": entries, "end": ["c"] if index == 3 else ["b"] if index == 4 else []})
+    steps.append({"step": 6, "entries": [{"id": "d", "tokens": d, "want": [0, 45, 89]}], "end": ["d"]})
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    result = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype,
+         "--out", str(out), "--max-tokens", str(1 + 75 + 133)],
+        input="\n".join(json.dumps(step) for step in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert result.returncode == 0, result.stderr
+    assert result.stdout.split() == [word for step in steps for word in ("done", str(step["step"]))]
+    read = lambda step: torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, config["vocab"])).double()
+    close(read(0), torch.stack([want["a"][0], want["b"][0], want["b"][69], want["c"][5], want["c"][128]]), dtype,
+          record_property, "prompts together", slack=2.0)
+    close(read(2), torch.stack([want["b"][71], want["c"][130]]), dtype, None, "decoded together", slack=2.0)
+    assert not (out / "3.f32").exists()                      # nothing was wanted in that step
+    close(read(5), want["b"][74:75], dtype, None, "the last one alone", slack=2.0)
+    close(read(6), want["d"][[0, 45, 89]], dtype, None, "on reused pages", slack=2.0)
