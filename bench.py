@@ -340,7 +340,7 @@ def qwen3_shape(width: int, layers: int = 4) -> dict:
 
 
 KERNEL_CLASSES = (
-    ("products", ("gemm_", "library_mm", "gemm_heads")),
+    ("products", ("gemm_", "library_mm", "library_bmm", "gemm_heads")),
     ("prompt attention", ("attention_prefill",)),
     ("decode attention", ("attention_decode", "latent_attention")),
     ("recurrence", ("gated_recurrence",)),

@@ -495,8 +495,10 @@ __global__ void __launch_bounds__(ROW_WARPS == 4 ? 256 : 128, 2) diff_attention_
     const bf16* v_cache = (const bf16*)a.v_cache;
     const int* table = g.table + (long long)slot * g.pages_per_seq;
     auto page_of = [&](int tile) { return tile < kept_tiles ? tile : low_page + tile - kept_tiles; };
-    auto load_tile = [&](int tile, int buffer) {
-        const long long at = ((long long)table[page_of(tile)] * g.kv_heads + kv_head) << 6;
+    // A tile's page id is read from the block table an iteration before the tile is asked for, so that the
+    // copies of the next tile do not wait for that read.
+    auto load_tile = [&](int page_id, int buffer) {
+        const long long at = ((long long)page_id * g.kv_heads + kv_head) << 6;
         const bf16* keys = k_cache + at * (2 * DIM);
         const bf16* values = v_cache + at * VDIM;
         bf16* k_to = k_s + buffer * TILE * KS;
@@ -533,7 +535,8 @@ __global__ void __launch_bounds__(ROW_WARPS == 4 ? 256 : 128, 2) diff_attention_
             for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
     }
 
-    if (first_tile < end_tile) load_tile(first_tile, 0);
+    if (first_tile < end_tile) load_tile(table[page_of(first_tile)], 0);
+    int next_page_id = first_tile + 1 < end_tile ? table[page_of(first_tile + 1)] : 0;
     // The block's query rows (while the first tile is on its way): row r is token t0 + r / group, head
     // kv_head * group + r % group.
     const bf16* q = (const bf16*)a.q;
@@ -548,7 +551,8 @@ __global__ void __launch_bounds__(ROW_WARPS == 4 ? 256 : 128, 2) diff_attention_
     for (int tile = first_tile; tile < end_tile; ++tile) {
         const int buffer = (tile - first_tile) & 1;
         if (tile + 1 < end_tile) {
-            load_tile(tile + 1, buffer ^ 1);
+            load_tile(next_page_id, buffer ^ 1);
+            if (tile + 2 < end_tile) next_page_id = table[page_of(tile + 2)];
             asm volatile("cp.async.wait_group 1;");
         } else {
             asm volatile("cp.async.wait_group 0;");

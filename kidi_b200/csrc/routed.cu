@@ -232,7 +232,8 @@ KIDI_API int kidi_expert_slots(const void* x, int dtype, const void* gate_up, co
 }
 
 // ------------------------------------------------------ gather / combine
-// gathered[i] = x[order[i] / top] * (weight[order[i]] or 1): the slots' input rows in the order of their experts.
+// gathered[i] = x[order[i] / top] * (weight[order[i]] or 1): the slots' input rows in the order of their experts
+// (order[i] < 0: a row of zeros, where every expert's rows are padded to one count).
 template <typename T>
 __global__ void gather_slots_kernel(const T* __restrict__ x, const int* __restrict__ order, const float* __restrict__ weight,
                                     T* __restrict__ gathered, long long total, int top, int hidden, int weight_on_input) {
@@ -241,6 +242,7 @@ __global__ void gather_slots_kernel(const T* __restrict__ x, const int* __restri
     const long long i = index / hidden;
     const int c = (int)(index - i * hidden);
     const int slot = order[i];
+    if (slot < 0) { gathered[index] = from_float<T>(0.f); return; }          // a padding row
     const float w = weight_on_input ? weight[slot] : 1.f;
     gathered[index] = from_float<T>(to_float(x[(long long)(slot / top) * hidden + c]) * w);
 }
@@ -272,8 +274,9 @@ __global__ void gather_slots_bf16x8_kernel(const bf16* __restrict__ x, const int
     const long long i = index / per_row;
     const int c = (int)(index - i * per_row) << 3;
     const int slot = order[i];
-    uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)(slot / top) * hidden + c);
-    if (weight_on_input) {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);                                  // a padding row stays zero
+    if (slot >= 0) raw = *reinterpret_cast<const uint4*>(x + (long long)(slot / top) * hidden + c);
+    if (slot >= 0 && weight_on_input) {
         const float w = weight[slot];
         __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll

@@ -68,7 +68,8 @@ def expert_slots(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, cho
 
 
 def gather_slots(x: torch.Tensor, order: torch.Tensor, weight: torch.Tensor, top: int, weight_on_input: bool) -> torch.Tensor:
-    """Row i of the result is x[order[i] // top] (times weight[order[i]] when the weight is on the input)."""
+    """Row i of the result is x[order[i] // top] (times weight[order[i]] when the weight is on the input); zeros
+    where order[i] is negative."""
     slots, hidden = order.shape[0], x.shape[1]
     out = torch.empty((slots, hidden), dtype=x.dtype, device=x.device)
     _check(library().kidi_gather_slots(x.data_ptr(), dtype_code(x.dtype), order.data_ptr(), weight.data_ptr(),

@@ -14,8 +14,10 @@ tensors, [experts, 2 * expert_size, hidden] (gate rows, then up rows) and [exper
 
 Steps of few rows, steps inside a captured decode graph, and every step of the 32-bit engine read the
 chosen experts' weights through the choice on the device (no host round trip). Prompts of the bfloat16
-engine sort the (row, choice) pairs by expert on the host, gather the scaled rows and run each expert's
-rows through the ordinary products.
+engine sort the (row, choice) pairs by expert on the host and gather the scaled rows; every expert's rows are
+then padded to one count and run through two batched products of the vendor library, or, where one expert has
+far more rows than the others or the widths are no multiples of 8, each expert's rows through the ordinary
+products.
 """
 from __future__ import annotations
 
@@ -68,7 +70,7 @@ class RoutedExperts(Part):
             both.append((name + self.gate_name, (self.inter, self.hidden)))
             both.append((name + self.up_name, (self.inter, self.hidden)))
             down.append((name + self.down_name, (self.hidden, self.inter)))
-        return [ParamSpec(self.router_name, (self.experts, self.hidden), init=("normal", 0.5)),
+        return [ParamSpec(self.router_name, (self.experts, self.hidden)),
                 ParamSpec("experts.gate_up", (self.experts * 2 * self.inter, self.hidden), sources=tuple(both)),
                 ParamSpec("experts.down", (self.experts * self.hidden, self.inter), sources=tuple(down))]
 
@@ -93,6 +95,25 @@ class RoutedExperts(Part):
         order = np.argsort(picked, kind="stable").astype(np.int32)
         counts = np.bincount(picked, minlength=self.experts)
         place = np.empty(slots, dtype=np.int32)
+        most = int(-(-int(counts.max()) // 8) * 8)
+        if self.hidden % 8 == 0 and self.inter % 8 == 0 and self.experts * most <= 3 * slots:
+            # Every expert's rows padded to one count: two batched products of the vendor library and one gate
+            # for all experts (taken unless one expert has far more rows than the others).
+            begins = np.concatenate([[0], np.cumsum(counts)[:-1]])
+            experts_sorted = picked[order]
+            at = (experts_sorted * most + (np.arange(slots) - begins[experts_sorted])).astype(np.int32)
+            padded = np.full(self.experts * most, -1, dtype=np.int32)
+            padded[at] = order
+            place[order] = at
+            both_tables = torch.from_numpy(np.concatenate([padded, place])).to(x.device)
+            gathered = routed.gather_slots(x, both_tables[:padded.size], weight, self.top, self.weight_on_input)
+            both = torch.bmm(gathered.view(self.experts, most, self.hidden), self.gate_up.transpose(1, 2))
+            ops.note("library_bmm")
+            mid = ops.silu_gate(both.view(self.experts * most, 2 * self.inter))
+            result = torch.bmm(mid.view(self.experts, most, self.inter), self.down.transpose(1, 2))
+            ops.note("library_bmm")
+            return routed.combine_slots(result.view(self.experts * most, self.hidden), both_tables[padded.size:], weight,
+                                        rows, self.top, self.weight_on_input)
         place[order] = np.arange(slots, dtype=np.int32)
         both = torch.from_numpy(np.concatenate([order, place])).to(x.device)
         gathered = routed.gather_slots(x, both[:slots], weight, self.top, self.weight_on_input)

@@ -85,15 +85,17 @@ def test_the_small_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,rows", [(6, 2, 5), (3, 3, 300), (16, 1, 200), (9, 4, 64)])
-def test_routed_experts_alone(dtype, experts, top, rows):
+@pytest.mark.parametrize("experts,top,rows,inter", [(6, 2, 5, 24), (3, 3, 300, 24), (16, 1, 200, 24), (9, 4, 64, 24),
+                                                     (4, 2, 150, 20)])
+def test_routed_experts_alone(dtype, experts, top, rows, inter):
     """The router's choice (sigmoid scores, the largest first, the weight on the expert's input) and the experts,
-    through the choice on the device and, for many rows in bfloat16, sorted by expert: against the plain function."""
+    through the choice on the device and, for many rows in bfloat16, sorted by expert (padded to one count and
+    batched, or expert by expert where the widths are no multiples of 8): against the plain function."""
     from types import SimpleNamespace
     from kidi_b200.parts.base import BuildEnv
     from kidi_b200.parts.routed import RoutedExperts
     from kidi_b200.parts.spec import PartSpec
-    hidden, inter = 40, 24
+    hidden = 40
     generator = torch.Generator().manual_seed(experts * 10 + top)
     w = {"m.router": torch.randn(experts, hidden, generator=generator) * 0.6}
     for e in range(experts):
@@ -112,9 +114,17 @@ def test_routed_experts_alone(dtype, experts, top, rows):
     part.bind({"router": w["m.router"].cuda(), "experts.gate_up": both, "experts.down": down})
     tolerance = 2e-5 if dtype == torch.float32 else 0.08
     scale = float(want.abs().max())
+    from kidi_b200.kernels import ops
     for decode in (False, True):                          # the sorted path (many bfloat16 rows), and through the choice
         ctx = SimpleNamespace(plan=SimpleNamespace(is_decode=decode))
-        found = part.forward(h.cuda(), ctx).double().cpu()
+        with ops.record_launches() as names:
+            found = part.forward(h.cuda(), ctx).double().cpu()
+        if dtype == torch.bfloat16 and not decode and rows * top > 128:
+            batched = names.count("library_bmm")          # unless one expert has far more rows than the others
+            assert batched == 0 if inter % 8 else batched == 2 if top == experts else batched in (0, 2)
+            assert "expert_slots" not in names
+        else:
+            assert "expert_slots" in names
         # a row whose choice is a close call may take another expert in bfloat16: at most a few rows differ
         bad = ((found - want).abs().max(-1).values > tolerance * scale).sum()
         assert int(bad) <= (0 if dtype == torch.float32 else max(1, rows // 50)), (decode, int(bad))
