@@ -33,7 +33,7 @@
 #define KIDI_DIFF_VDIM 0
 #endif
 
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 32;
 
 struct DiffGeometry {
     const int* table;      // [slots + 1, pages_per_seq]

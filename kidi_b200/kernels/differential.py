@@ -15,7 +15,7 @@ from . import ops
 from .ops import _check, c_float, c_int, c_longlong, c_void_p, dtype_code
 
 FORCE_GENERAL = os.environ.get("KIDI_B200_GENERIC_ATTENTION", "0") == "1"
-MAX_TAPS = 8
+MAX_TAPS = 32
 
 
 class DiffGeometry(ctypes.Structure):

@@ -47,7 +47,7 @@ SMALL_B = model(131, 72, 700, 3e-6, 0.0, [
     attention(6, 2, 12, 20, 3, 0.4, 0.3, window=17, keep_first=5, mlp=routed(5, 1, 20)),
     attention(2, 2, 16, 16, 2, 0.2, 0.35, window=200, keep_first=70, mlp=dense(100, 3.0)),
     attention(1, 1, 40, 24, 1, 0.6, 0.2, window=64, keep_first=1, mlp=routed(3, 3, 16)),     # one tap: a weight a channel
-    attention(5, 1, 8, 12, 3, 0.8, 0.5, mlp=dense(64, 0.7)),
+    attention(5, 1, 8, 12, 9, 0.8, 0.5, mlp=dense(64, 0.7)),                                  # nine taps
 ])
 
 # widths that the tensor-core kernels take: groups of 2, 8, 1 and 3 heads, maps of 32, 64, 128 and 16
